@@ -1,0 +1,164 @@
+// Embedding gather, RMS norm, SwiGLU, and rotary position encoding fused with the
+// append of keys and values into the paged cache.  Each kernel computes in float
+// and converts only when it stores.
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding
+// out[t, :] = table[ids[t], :] * scale.  Ids are validated by the caller (host ids)
+// or produced by the sampler (always in range); an id out of range sets *status
+// and writes zeros instead of reading outside the table.
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ out,
+                             int d, int V, float scale, int* status) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < V;
+    if (!ok && threadIdx.x == 0 && status) atomicExch(status, 1);
+    const TW* row = table + (size_t)(ok ? id : 0) * d;
+    float* o = out + (size_t)t * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = ok ? ik_ld(row, i) * scale : 0.f;
+}
+
+IK_EXPORT int ik_embed(const int* ids, const void* table, int table_dtype, float* out, int T, int d, int V,
+                       float scale, int* status, cudaStream_t stream) {
+    if (T < 0 || d <= 0 || V <= 0) return IK_BAD_ARGUMENT;
+    if (T == 0) return IK_OK;
+    if (table_dtype == IK_F32)
+        embed_kernel<float><<<T, 256, 0, stream>>>(ids, (const float*)table, out, d, V, scale, status);
+    else if (table_dtype == IK_BF16)
+        embed_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, d, V, scale, status);
+    else
+        return IK_BAD_ARGUMENT;
+    IK_LAUNCH_STATUS();
+}
+
+// ------------------------------------------------------------------ RMS norm
+// y = x * (1 / sqrt(mean(x^2) + eps)) * w, one block per output row.  rows_in selects
+// input rows when given (the final norm runs only on the rows whose logits are wanted).
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows_in,
+                               const float* __restrict__ w, TO* __restrict__ out, int d, float eps) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const float* a = x + (size_t)(rows_in ? rows_in[r] : r) * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += 256) { float v = a[i]; ss = fmaf(v, v, ss); }
+    ss = ik_block_sum<256>(ss, red);
+    const float s = 1.0f / sqrtf(ss / (float)d + eps);
+    TO* o = out + (size_t)r * d;
+    for (int i = threadIdx.x; i < d; i += 256) ik_st(o, i, a[i] * s * w[i]);
+}
+
+IK_EXPORT int ik_rmsnorm(const float* x, const int* rows_in, const float* w, void* out, int out_dtype, int rows,
+                         int d, float eps, cudaStream_t stream) {
+    if (rows < 0 || d <= 0) return IK_BAD_ARGUMENT;
+    if (rows == 0) return IK_OK;
+    if (out_dtype == IK_F32)
+        rmsnorm_kernel<float><<<rows, 256, 0, stream>>>(x, rows_in, w, (float*)out, d, eps);
+    else if (out_dtype == IK_BF16)
+        rmsnorm_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>(x, rows_in, w, (__nv_bfloat16*)out, d, eps);
+    else
+        return IK_BAD_ARGUMENT;
+    IK_LAUNCH_STATUS();
+}
+
+// ------------------------------------------------------------------ SwiGLU
+// in: [T, 2*ff] float, gate in columns [0, ff), up in [ff, 2ff).  out[t, j] = silu(g) * u.
+template <typename TO>
+__global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out, int ff, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / ff;
+        const int j = (int)(idx - t * ff);
+        const float g = gu[t * 2 * ff + j], u = gu[t * 2 * ff + ff + j];
+        ik_st(out, idx, g / (1.0f + expf(-g)) * u);
+    }
+}
+
+IK_EXPORT int ik_swiglu(const float* gate_up, void* out, int out_dtype, int T, int ff, cudaStream_t stream) {
+    if (T < 0 || ff <= 0) return IK_BAD_ARGUMENT;
+    if (T == 0) return IK_OK;
+    const size_t total = (size_t)T * ff;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (out_dtype == IK_F32)
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>(gate_up, (float*)out, ff, total);
+    else if (out_dtype == IK_BF16)
+        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(gate_up, (__nv_bfloat16*)out, ff, total);
+    else
+        return IK_BAD_ARGUMENT;
+    IK_LAUNCH_STATUS();
+}
+
+// ------------------------------------------------------------------ rotary + cache append
+// qkv: [T, (nh + 2 nkv) * hd] float, q heads first, then k heads, then v heads.
+// One block per (token, head).  q heads are rotated and stored to q_out [T, nh*hd];
+// k heads are rotated and stored into the token's place in the key pages; v heads are
+// stored into the value pages.  A page holds page_size positions of every kv head:
+// pages[page][kv_head][position in page][hd].  The page of position p of sequence s is
+// table[s * table_stride + p / page_size].
+//
+// Angle = float(pos) * inv_freq[i] as a single float multiply; cosf/sinf are the accurate
+// functions.  pairing 0 rotates (i, i + rot/2), pairing 1 rotates (2i, 2i + 1); dimensions
+// from rot upward pass through.
+template <typename TQ, typename TC>
+__global__ void rope_append_kernel(const float* __restrict__ qkv, TQ* __restrict__ q_out, TC* __restrict__ k_pages,
+                                   TC* __restrict__ v_pages, const int* __restrict__ token_seq,
+                                   const int* __restrict__ token_pos, const int* __restrict__ table, int table_stride,
+                                   const float* __restrict__ inv_freq, int nh, int nkv, int hd, int rot, int pairing,
+                                   int page_size, int n_pages, int write_cache, int* status) {
+    const int t = blockIdx.x, head = blockIdx.y;
+    const int pos = token_pos[t];
+    const float* src = qkv + (size_t)t * (nh + 2 * nkv) * hd + (size_t)head * hd;
+    const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
+    if (!is_q && !write_cache) return;
+    size_t dst_off = 0;
+    if (!is_q) {
+        const int seq = token_seq[t];
+        const int page = table[(size_t)seq * table_stride + pos / page_size];
+        if (page < 0 || page >= n_pages) {          // never write outside the pool
+            if (threadIdx.x == 0 && status) atomicExch(status, 2);
+            return;
+        }
+        const int kvh = is_k ? head - nh : head - nh - nkv;
+        dst_off = (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * hd;
+    }
+    if (is_q || is_k) {
+        const int half = rot / 2;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const int i0 = pairing == 0 ? i : 2 * i, i1 = pairing == 0 ? i + half : 2 * i + 1;
+            const float ang = __fmul_rn((float)pos, inv_freq[i]);
+            const float c = cosf(ang), s = sinf(ang);
+            const float a = src[i0], b = src[i1];
+            const float r0 = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+            const float r1 = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
+            if (is_q) { ik_st(q_out, (size_t)t * nh * hd + (size_t)head * hd + i0, r0); ik_st(q_out, (size_t)t * nh * hd + (size_t)head * hd + i1, r1); }
+            else { ik_st(k_pages, dst_off + i0, r0); ik_st(k_pages, dst_off + i1, r1); }
+        }
+        for (int i = rot + threadIdx.x; i < hd; i += blockDim.x) {
+            if (is_q) ik_st(q_out, (size_t)t * nh * hd + (size_t)head * hd + i, src[i]);
+            else ik_st(k_pages, dst_off + i, src[i]);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hd; i += blockDim.x) ik_st(v_pages, dst_off + i, src[i]);
+    }
+}
+
+IK_EXPORT int ik_rope_append(const float* qkv, void* q_out, int q_dtype, void* k_pages, void* v_pages, int cache_dtype,
+                             const int* token_seq, const int* token_pos, const int* table, int table_stride,
+                             const float* inv_freq, int T, int nh, int nkv, int hd, int rot, int pairing,
+                             int page_size, int n_pages, int write_cache, int* status, cudaStream_t stream) {
+    if (T < 0 || nh <= 0 || nkv <= 0 || hd <= 0 || rot < 0 || rot > hd || (rot & 1) || page_size <= 0) return IK_BAD_ARGUMENT;
+    if (rot > 0 && !inv_freq) return IK_BAD_ARGUMENT;
+    if (T == 0) return IK_OK;
+    dim3 grid(T, nh + 2 * nkv);
+    const int threads = 64;
+#define IK_ROPE(TQ, TC)                                                                                             \
+    rope_append_kernel<TQ, TC><<<grid, threads, 0, stream>>>(qkv, (TQ*)q_out, (TC*)k_pages, (TC*)v_pages, token_seq, \
+        token_pos, table, table_stride, inv_freq, nh, nkv, hd, rot, pairing, page_size, n_pages, write_cache, status)
+    if (q_dtype == IK_F32 && cache_dtype == IK_F32) IK_ROPE(float, float);
+    else if (q_dtype == IK_BF16 && cache_dtype == IK_BF16) IK_ROPE(__nv_bfloat16, __nv_bfloat16);
+    else if (q_dtype == IK_F32 && cache_dtype == IK_BF16) IK_ROPE(float, __nv_bfloat16);
+    else if (q_dtype == IK_BF16 && cache_dtype == IK_F32) IK_ROPE(__nv_bfloat16, float);
+    else return IK_BAD_ARGUMENT;
+#undef IK_ROPE
+    IK_LAUNCH_STATUS();
+}

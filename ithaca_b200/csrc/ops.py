@@ -1,0 +1,217 @@
+"""Python side of the kernel library: argument checks, pointers, the current stream.
+
+Every function launches on torch's current CUDA stream and allocates nothing but its
+declared outputs.  A non-zero status from the library raises ``KernelError``.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+_vp, _i, _f, _u64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_ulonglong
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} is not supported by the kernels (float32, bfloat16)") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, found {t.dtype}")
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status == -1:
+        raise KernelError(f"{what}: bad argument")
+    if status == -2:
+        raise KernelError(f"{what}: these sizes are not supported by this kernel")
+    raise KernelError(f"{what}: CUDA error {status} at launch")
+
+
+_SIGNATURES = {
+    "ik_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _f, _vp, _vp],
+    "ik_rmsnorm": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
+    "ik_swiglu": [_vp, _vp, _i, _i, _i, _vp],
+    "ik_rope_append": [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "ik_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "ik_attention_simt": [_vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp],
+    "ik_argmax": [_vp, _i, _vp, _i, _i, _vp],
+    "ik_sample": [_vp, _i, _vp, _vp, _i, _i, _f, _i, _f, _f, _vp, _i, _u64, _vp, _vp, _vp],
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded kernel library; built on first use.  Raises if that fails."""
+    global _lib
+    if _lib is None:
+        l = build.core()
+        for name, sig in _SIGNATURES.items():
+            fn = getattr(l, name)
+            fn.argtypes = sig
+            fn.restype = _i
+        _lib = l
+    return _lib
+
+
+# ---------------------------------------------------------------------------------------------
+def embed(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0, status: Optional[torch.Tensor] = None,
+          out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need(ids, "ids", torch.int32)
+    _need(table, "table")
+    T, (V, d) = ids.numel(), table.shape
+    if out is None:
+        out = torch.empty((T, d), dtype=torch.float32, device=ids.device)
+    _check(lib().ik_embed(_ptr(ids), _ptr(table), _code(table), _ptr(out), T, d, V, scale, _ptr(status), _stream()),
+           "embed")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            rows_in: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need(x, "x", torch.float32)
+    _need(weight, "weight", torch.float32)
+    d = x.shape[-1]
+    if weight.numel() != d:
+        raise KernelError(f"rmsnorm: weight has {weight.numel()} elements, rows have {d}")
+    rows = x.numel() // d if rows_in is None else rows_in.numel()
+    if rows_in is not None:
+        _need(rows_in, "rows_in", torch.int32)
+    if out is None:
+        out = torch.empty((rows, d), dtype=out_dtype, device=x.device)
+    _check(lib().ik_rmsnorm(_ptr(x), _ptr(rows_in), _ptr(weight), _ptr(out), _code(out), rows, d, eps, _stream()),
+           "rmsnorm")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need(gate_up, "gate_up", torch.float32)
+    T, ff2 = gate_up.shape
+    if ff2 % 2:
+        raise KernelError("swiglu: the input needs an even number of columns (gate then up)")
+    if out is None:
+        out = torch.empty((T, ff2 // 2), dtype=out_dtype, device=gate_up.device)
+    _check(lib().ik_swiglu(_ptr(gate_up), _ptr(out), _code(out), T, ff2 // 2, _stream()), "swiglu")
+    return out
+
+
+def rope_append(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                token_seq: torch.Tensor, token_pos: torch.Tensor, table: torch.Tensor,
+                inv_freq: Optional[torch.Tensor], n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
+                pairing: int, write_cache: bool, status: Optional[torch.Tensor]) -> None:
+    """k_pages / v_pages: [n_pages, n_kv_heads, page_size, head_dim] of one layer."""
+    _need(qkv, "qkv", torch.float32)
+    _need(q_out, "q_out")
+    _need(k_pages, "k_pages")
+    _need(v_pages, "v_pages")
+    _need(table, "table", torch.int32)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim:
+        raise KernelError("rope_append: qkv has the wrong width")
+    n_pages, nkv, page_size, hd = k_pages.shape
+    if nkv != n_kv_heads or hd != head_dim or v_pages.shape != k_pages.shape or v_pages.dtype != k_pages.dtype:
+        raise KernelError("rope_append: the pages do not match the head sizes")
+    _check(lib().ik_rope_append(_ptr(qkv), _ptr(q_out), _code(q_out), _ptr(k_pages), _ptr(v_pages), _code(k_pages),
+                                _ptr(token_seq), _ptr(token_pos), _ptr(table), table.stride(0), _ptr(inv_freq), T,
+                                n_heads, n_kv_heads, head_dim, rotary_dim, pairing, page_size, n_pages,
+                                1 if write_cache else 0, _ptr(status), _stream()), "rope_append")
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=torch.float32,
+              accumulate: bool = False) -> torch.Tensor:
+    """out[M, N] (+)= x[M, K] @ w[N, K]^T on the CUDA cores, float accumulation in ascending k."""
+    _need(x, "x", contiguous=False)
+    _need(w, "w", contiguous=False)
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2 or x.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError(f"gemm: shapes {tuple(x.shape)} x {tuple(w.shape)}^T do not match or rows are not contiguous")
+    if out is None:
+        if accumulate:
+            raise KernelError("gemm: accumulate needs an output to add to")
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _need(out, "out", contiguous=False)
+    if out.shape != (M, N) or out.stride(1) != 1:
+        raise KernelError("gemm: the output has the wrong shape")
+    _check(lib().ik_gemm_simt(_ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), M, N, K, x.stride(0),
+                              w.stride(0), out.stride(0), 1 if accumulate else 0, _stream()), "gemm_simt")
+    return out
+
+
+def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, token_seq: torch.Tensor,
+                   token_pos: torch.Tensor, table: torch.Tensor, n_heads: int, scale: float, window: int,
+                   status: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need(q, "q")
+    _need(k_pages, "k_pages")
+    _need(v_pages, "v_pages")
+    _need(table, "table", torch.int32)
+    n_pages, nkv, page_size, hd = k_pages.shape
+    T = q.shape[0]
+    if q.shape[1] != n_heads * hd:
+        raise KernelError("attention: q has the wrong width")
+    if out is None:
+        out = torch.empty_like(q)
+    _check(lib().ik_attention_simt(_ptr(q), _code(q), _ptr(k_pages), _ptr(v_pages), _code(k_pages), _ptr(out),
+                                   _code(out), _ptr(token_seq), _ptr(token_pos), _ptr(table), table.stride(0), T,
+                                   n_heads, nkv, hd, scale, window, page_size, n_pages, _ptr(status), _stream()),
+           "attention_simt")
+    return out
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need(logits, "logits", torch.float32, contiguous=False)
+    rows, V = logits.shape
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    _check(lib().ik_argmax(_ptr(logits), logits.stride(0), _ptr(out), rows, V, _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, repetition_penalty: float,
+           recent: Optional[torch.Tensor], seed: int, streams: torch.Tensor, counters: torch.Tensor,
+           out: Optional[torch.Tensor] = None, work: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need(logits, "logits", torch.float32, contiguous=False)
+    _need(streams, "streams", torch.int32)
+    _need(counters, "counters", torch.int32)
+    rows, V = logits.shape
+    n_recent = 0
+    if recent is not None:
+        _need(recent, "recent", torch.int32)
+        n_recent = recent.shape[1]
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    if work is None:
+        work = torch.empty((rows, V), dtype=torch.float32, device=logits.device)
+    _check(lib().ik_sample(_ptr(logits), logits.stride(0), _ptr(work), _ptr(out), rows, V, temperature, top_k, top_p,
+                           repetition_penalty, _ptr(recent), n_recent, seed & 0xFFFFFFFFFFFFFFFF, _ptr(streams),
+                           _ptr(counters), _stream()), "sample")
+    return out

@@ -1,0 +1,240 @@
+// Sampling on the device: one block per row of logits.
+//
+// The rule is the reference's (src/chat.cpp:124-145): each recent id is penalised
+// (l > 0 ? l / pen : l * pen, once per occurrence); temperature <= 0 takes the largest
+// logit; otherwise the k = clamp(top_k, 1, V) largest are kept, weighted
+// exp((l - max) / temperature), and of those the shortest prefix in descending order whose
+// share of the weight reaches top_p (the crossing one included).  One of the kept is
+// drawn with a uniform number.  Two things are this library's own: the uniform comes from
+// Philox-4x32-10 keyed by (seed) with counter (step, stream), so a sequence's draws do not
+// depend on what else is in the batch; and the kept candidates are walked in vocabulary
+// order (the same law as the reference's descending walk, without a sort).  Equal logits
+// are ordered by ascending id.  No sort is done anywhere: the k-th largest value and the
+// top_p boundary are found by bisection over the bits of an order-preserving integer key.
+#include <math.h>
+#include "common.cuh"
+
+namespace {
+
+constexpr int ST = 1024;
+
+__device__ __forceinline__ uint32_t okey(float v) {
+    const uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float unkey(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+__device__ __forceinline__ float philox_uniform(uint64_t seed, uint32_t stream, uint32_t counter) {
+    const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+    uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+    uint32_t c0 = counter, c1 = stream, c2 = 0, c3 = 0;
+    #pragma unroll
+    for (int r = 0; r < 10; r++) {
+        const uint32_t h0 = __umulhi(M0, c0), l0 = M0 * c0, h1 = __umulhi(M1, c2), l1 = M1 * c2;
+        const uint32_t n0 = h1 ^ c1 ^ k0, n2 = h0 ^ c3 ^ k1;
+        c0 = n0; c1 = l1; c2 = n2; c3 = l0;
+        k0 += W0; k1 += W1;
+    }
+    return ((float)(c0 >> 8) + 0.5f) * (1.0f / 16777216.0f);   // 24 bits: exact in float, inside (0, 1)
+}
+
+// Inclusive block scan (fixed order): lanes by shuffle, then the warp totals.
+template <typename T>
+__device__ __forceinline__ T block_scan_inclusive(T v, T* warp_tot /* [32] */, T* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    #pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        T n = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += n;
+    }
+    __syncthreads();
+    if (lane == 31) warp_tot[warp] = v;
+    __syncthreads();
+    T before = 0, all = 0;
+    #pragma unroll
+    for (int w = 0; w < ST / 32; w++) { const T x = warp_tot[w]; if (w < warp) before += x; all += x; }
+    *total = all;
+    return v + before;
+}
+
+struct Best { float v; int i; };
+__device__ __forceinline__ Best better(Best a, Best b) {      // larger value, then smaller index
+    return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
+}
+
+__device__ Best block_argmax(const float* w, int V, Best* sh /* [32] */) {
+    Best b{-INFINITY, 0x7fffffff};
+    for (int i = threadIdx.x; i < V; i += ST) b = better(b, Best{w[i], i});
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best n{__shfl_xor_sync(0xffffffffu, b.v, o), __shfl_xor_sync(0xffffffffu, b.i, o)};
+        b = better(b, n);
+    }
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = b;
+    __syncthreads();
+    Best r = sh[0];
+    for (int wv = 1; wv < ST / 32; wv++) r = better(r, sh[wv]);
+    return r;
+}
+
+__global__ void __launch_bounds__(ST)
+argmax_kernel(const float* __restrict__ logits, int ldl, int* __restrict__ out, int V) {
+    __shared__ Best sh[32];
+    const Best b = block_argmax(logits + (size_t)blockIdx.x * ldl, V, sh);
+    if (threadIdx.x == 0) out[blockIdx.x] = b.i;
+}
+
+struct Keep {                 // which candidates survive top-k and top-p
+    uint32_t tk; int need_k;  // key of the k-th largest; how many of the ties at tk are kept
+    uint32_t tp; int need_p;  // key at the top-p boundary; how many of the ties at tp are kept
+    bool use_p;
+};
+
+__global__ void __launch_bounds__(ST)
+sample_kernel(const float* __restrict__ logits, int ldl, float* __restrict__ work, int* __restrict__ out, int V,
+              float temperature, int top_k, float top_p, float rep_pen, const int* __restrict__ recent, int n_recent,
+              uint64_t seed, const int* __restrict__ streams, const int* __restrict__ counters) {
+    __shared__ Best shb[32];
+    __shared__ float shf[32];
+    __shared__ int shi[32];
+    __shared__ int chosen_thread;
+    __shared__ int last_thread;
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const float* l = logits + (size_t)row * ldl;
+    float* w = work + (size_t)row * V;
+
+    for (int i = tid; i < V; i += ST) w[i] = l[i];
+    __syncthreads();
+    if (rep_pen != 1.0f && tid == 0) {
+        for (int n = 0; n < n_recent; n++) {
+            const int id = recent[(size_t)row * n_recent + n];
+            if (id >= 0 && id < V) { const float v = w[id]; w[id] = v > 0.f ? v / rep_pen : v * rep_pen; }
+        }
+    }
+    __syncthreads();
+    const Best top = block_argmax(w, V, shb);
+    if (temperature <= 0.f) { if (tid == 0) out[row] = top.i; return; }
+
+    const int k = min(V, max(1, top_k));
+    const int per = (V + ST - 1) / ST, lo = min(V, tid * per), hi = min(V, lo + per);
+    const float inv_t = 1.0f / temperature, mx = top.v;
+    Keep kp{0u, V, 0u, V, false};
+
+    // ---- top-k: the largest key T with count{key >= T} >= k
+    if (k < V) {
+        uint32_t T = 0;
+        for (int b = 31; b >= 0; b--) {
+            const uint32_t cand = T | (1u << b);
+            int c = 0;
+            for (int i = tid; i < V; i += ST) c += okey(w[i]) >= cand;
+            int tot; block_scan_inclusive<int>(c, shi, &tot);
+            if (tot >= k) T = cand;
+        }
+        int c = 0;
+        for (int i = tid; i < V; i += ST) c += okey(w[i]) > T;
+        int n_gt; block_scan_inclusive<int>(c, shi, &n_gt);
+        kp.tk = T; kp.need_k = k - n_gt;
+    }
+    // rank of this thread's first tie at tk among all ties at tk, in id order
+    int tie_k_before;
+    {
+        int c = 0;
+        for (int i = lo; i < hi; i++) c += okey(w[i]) == kp.tk;
+        int tot; tie_k_before = block_scan_inclusive<int>(c, shi, &tot) - c;
+    }
+    int tie_p_before = 0;
+
+    // mass of the kept candidates with key >= bound (bound_incl) or > bound, summed in id order per thread
+    auto kept_mass = [&](uint32_t bound, bool strict, const Keep& kk, int tkb, int tpb) {
+        float s = 0.f; int rk = tkb, rp = tpb;
+        for (int i = lo; i < hi; i++) {
+            const uint32_t key = okey(w[i]);
+            bool in = key > kk.tk || (key == kk.tk && rk < kk.need_k);
+            if (key == kk.tk) rk++;
+            if (kk.use_p) { in = in && (key > kk.tp || (key == kk.tp && rp < kk.need_p)); if (key == kk.tp) rp++; }
+            if (in && (strict ? key > bound : key >= bound)) s += expf((w[i] - mx) * inv_t);
+        }
+        return s;
+    };
+
+    // ---- top-p over the top-k survivors
+    if (top_p < 1.0f) {
+        float total; block_scan_inclusive<float>(kept_mass(0u, false, kp, tie_k_before, 0), shf, &total);
+        const float target = top_p * total;
+        uint32_t T = 0;
+        for (int b = 31; b >= 0; b--) {
+            const uint32_t cand = T | (1u << b);
+            float m; block_scan_inclusive<float>(kept_mass(cand, false, kp, tie_k_before, 0), shf, &m);
+            if (m >= target) T = cand;
+        }
+        float mass_gt; block_scan_inclusive<float>(kept_mass(T, true, kp, tie_k_before, 0), shf, &mass_gt);
+        int c = 0;
+        { int rk = tie_k_before;
+          for (int i = lo; i < hi; i++) { const uint32_t key = okey(w[i]);
+              const bool in = key > kp.tk || (key == kp.tk && rk < kp.need_k);
+              if (key == kp.tk) rk++;
+              c += in && key == T; } }
+        int ties; block_scan_inclusive<int>(c, shi, &ties);
+        const float wt = expf((unkey(T) - mx) * inv_t);
+        int n = 1;
+        if (ties > 1 && wt > 0.f) {
+            n = (int)fminf((float)ties, fmaxf(1.f, ceilf((target - mass_gt) / wt)));
+            while (n > 1 && mass_gt + (float)(n - 1) * wt >= target) n--;
+            while (n < ties && mass_gt + (float)n * wt < target) n++;
+        }
+        int c2 = 0;
+        for (int i = lo; i < hi; i++) c2 += okey(w[i]) == T;
+        int tot2; tie_p_before = block_scan_inclusive<int>(c2, shi, &tot2) - c2;
+        kp.tp = T; kp.need_p = n; kp.use_p = true;
+    }
+
+    // ---- draw in vocabulary order
+    const float mine = kept_mass(0u, false, kp, tie_k_before, tie_p_before);
+    float total;
+    const float incl = block_scan_inclusive<float>(mine, shf, &total);
+    const float u = philox_uniform(seed, (uint32_t)streams[row], (uint32_t)counters[row]);
+    const float r = fminf(u * total, total);
+    if (tid == 0) { chosen_thread = ST; last_thread = -1; }
+    __syncthreads();
+    if (mine > 0.f) { atomicMax(&last_thread, tid); if (r <= incl) atomicMin(&chosen_thread, tid); }
+    __syncthreads();
+    // the first thread whose running sum reaches r; if rounding left nobody, the last thread that kept anything
+    const int owner = chosen_thread < ST ? chosen_thread : last_thread;
+    if (tid == owner) {
+        float acc = incl - mine; int rk = tie_k_before, rp = tie_p_before, pick = -1, last = -1;
+        for (int i = lo; i < hi; i++) {
+            const uint32_t key = okey(w[i]);
+            bool in = key > kp.tk || (key == kp.tk && rk < kp.need_k);
+            if (key == kp.tk) rk++;
+            if (kp.use_p) { in = in && (key > kp.tp || (key == kp.tp && rp < kp.need_p)); if (key == kp.tp) rp++; }
+            if (!in) continue;
+            last = i;
+            acc += expf((w[i] - mx) * inv_t);
+            if (r <= acc) { pick = i; break; }
+        }
+        out[row] = pick >= 0 ? pick : (last >= 0 ? last : top.i);
+    }
+}
+
+}  // namespace
+
+IK_EXPORT int ik_argmax(const float* logits, int ldl, int* out, int rows, int V, cudaStream_t stream) {
+    if (rows < 0 || V <= 0 || ldl < V) return IK_BAD_ARGUMENT;
+    if (rows == 0) return IK_OK;
+    argmax_kernel<<<rows, ST, 0, stream>>>(logits, ldl, out, V);
+    IK_LAUNCH_STATUS();
+}
+
+// work: [rows, V] floats of scratch owned by the caller.  recent: [rows, n_recent] ids, -1 = empty.
+IK_EXPORT int ik_sample(const float* logits, int ldl, float* work, int* out, int rows, int V, float temperature,
+                        int top_k, float top_p, float rep_pen, const int* recent, int n_recent,
+                        unsigned long long seed, const int* streams, const int* counters, cudaStream_t stream) {
+    if (rows < 0 || V <= 0 || ldl < V || n_recent < 0 || !(rep_pen > 0.f) || !(top_p > 0.f)) return IK_BAD_ARGUMENT;
+    if (rows == 0) return IK_OK;
+    sample_kernel<<<rows, ST, 0, stream>>>(logits, ldl, work, out, V, temperature, top_k, top_p, rep_pen, recent,
+                                           n_recent, (uint64_t)seed, streams, counters);
+    IK_LAUNCH_STATUS();
+}

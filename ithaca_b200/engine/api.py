@@ -1,0 +1,119 @@
+"""The Python entry point: a model folder (or a configuration and a seed) in, tokens out.
+
+The reference has no Python surface; its programmatic entry is ``Model::load`` +
+``Chat::generate`` (src/model.cpp:45, src/chat.cpp:292) behind the command line
+(src/main.cpp:1033-1144).  ``Engine`` is that pair: it loads the model the
+folder's ``config.json`` names, owns the cache, and offers ``step`` (the step
+function) and ``generate`` (the loop with sampling).  Option names are the
+reference's where it has them: ``ctx`` (``--ctx``), ``max_tokens``/``temp``/
+``top_k``/``top_p``/``rep_pen`` (``GenOpts``).
+"""
+from __future__ import annotations
+
+from typing import Any, Callable, Dict, List, Optional, Sequence, Union
+
+import torch
+
+from ..cache.cache import PAGE_SIZE, SequenceCache
+from ..config import config_from_dict
+from ..parts import Runtime
+from ..sampling.sampler import Sampler, SamplingOptions
+from ..weights.random_init import random_tensors
+from .generate import GenerationOptions, GenStats, generate_loop
+from .model import build_model, load_model, weight_manifest
+from .step import Stepper
+
+
+def _round_up(n: int, m: int) -> int:
+    return -(-n // m) * m
+
+
+class Engine:
+    def __init__(self, model_dir: Optional[str] = None, *, dtype: str = "bfloat16", device: str = "cuda:0",
+                 max_tokens: Optional[int] = None, max_slots: Optional[int] = None, ctx: Optional[int] = None,
+                 _model=None, _config=None):
+        """``max_tokens``: the most positions live sequences hold at any time, each rounded up
+        to a multiple of 64; it sizes the cache (default: 8 sequences of ``ctx``).
+        ``ctx``: the most positions one sequence may hold (default: the model's
+        ``max_position_embeddings``, as the reference caps ``--ctx`` at the trained
+        context, src/model.cpp:259)."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("ithaca_b200 runs on a CUDA device only; none is available")
+        torch.cuda.set_device(device)
+        self.runtime = Runtime(dtype=dtype, device=device)
+        if _model is None:
+            if model_dir is None:
+                raise ValueError("a model folder is needed")
+            _model, _config = load_model(model_dir, self.runtime)
+        self.model, self.config = _model, _config
+        spec = self.model.spec
+        self.context_length = min(ctx, spec.max_position) if ctx else spec.max_position
+        if max_tokens is None:
+            max_tokens = 8 * _round_up(min(self.context_length, 4096), PAGE_SIZE)
+        self.cache = SequenceCache(self.model.cache_requests(), max_tokens=max_tokens, max_slots=max_slots,
+                                   kv_dtype=self.runtime.kv_dtype, device=device)
+        self.stepper = Stepper(self.model, self.cache, max_position=self.context_length)
+        self.last_stats: Optional[GenStats] = None
+        self._sampler: Optional[Sampler] = None
+        self._decoder = None
+
+    @classmethod
+    def from_random(cls, config: Dict[str, Any], seed: int = 0, *, dtype: str = "bfloat16",
+                    weights_dtype: Optional[str] = None, device: str = "cuda:0", **kw) -> "Engine":
+        """A model with random weights made on the device (nothing is written to disk)."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("ithaca_b200 runs on a CUDA device only; none is available")
+        torch.cuda.set_device(device)
+        arch, cfg = config_from_dict(config)
+        runtime = Runtime(dtype=dtype, device=device)
+        tensors = random_tensors(weight_manifest(cfg.model_spec()), seed, weights_dtype or config.get("torch_dtype", "bfloat16"),
+                                 device=device)
+        model = build_model(arch, cfg, tensors, runtime)
+        eng = cls(None, dtype=dtype, device=device, _model=model, _config=cfg, **kw)
+        return eng
+
+    # -- the step function ---------------------------------------------------------------------
+    def alloc_slot(self) -> int:
+        return self.cache.alloc_slot()
+
+    def free_slot(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
+             want: Union[str, None, Sequence[Sequence[int]]] = "last") -> Optional[torch.Tensor]:
+        return self.stepper.step(slots, tokens, want)
+
+    # -- Backend of the generation loop --------------------------------------------------------
+    def free_slots(self) -> int:
+        return self.cache.max_slots - self.cache.table.n_slots_in_use()
+
+    def room_for(self, lengths: Sequence[int]) -> bool:
+        page = self.cache.page_size
+        need = sum(-(-n // page) for n in lengths)
+        return all(need <= pool.n_free for pool in self.cache.table.pools) if self.cache.table.pools else True
+
+    def step_and_sample(self, slots, tokens, streams, counters, recent) -> List[int]:
+        if self._decoder is not None and all(len(t) == 1 for t in tokens):
+            ids = self._decoder.step_and_sample(slots, tokens, streams, counters, recent, self._sampler)
+        else:
+            logits = self.stepper.step(slots, tokens, "last")
+            ids = self._sampler.sample(logits, streams, counters, recent)
+        host = ids.cpu()                      # waits for the step
+        self.stepper.check_status()
+        return host.tolist()
+
+    # -- generation ----------------------------------------------------------------------------
+    def generate(self, prompts: Sequence[Sequence[int]], options: Optional[GenerationOptions] = None,
+                 on_token: Optional[Callable[[int, int], bool]] = None, **kw) -> List[List[int]]:
+        """Generates for every prompt (lists of token ids); returns the new ids per prompt.
+        Keyword arguments are ``GenerationOptions`` fields.  Counters of the run are in
+        ``last_stats``."""
+        if options is None:
+            options = GenerationOptions(**kw)
+        elif kw:
+            raise ValueError("give either options or keyword arguments")
+        self._sampler = Sampler(options.sampling(), self.runtime.device)
+        out, stats = generate_loop(prompts, options, self, stop_token_ids=self.model.spec.stop_token_ids,
+                                   on_token=on_token)
+        self.last_stats = stats
+        return out

@@ -1,0 +1,111 @@
+"""The step function: a batch of sequences, each bringing its next tokens.
+
+The reference's ``Model::eval(toks, n)`` appends n tokens of its single sequence
+and returns the last token's logits; ``eval_all`` returns all n rows
+(src/model.h:85-90, src/model.cpp:1312).  Here one call serves a batch: every
+sequence brings one or more tokens (all prompts in one step, then one token each;
+mixtures are legal), the step runs exactly those tokens as one batch against the
+cache that earlier steps left, and returns float32 logits at the wanted places.
+
+Nothing is padded: activations are token-major [T, ...] with T the number of
+tokens the step brings, so what else is in the batch cannot change a row.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from ..cache.cache import SequenceCache
+from ..cache.pages import CacheError
+from .context import ContextBuilder, StepContext
+
+
+class StepError(ValueError):
+    pass
+
+
+class Stepper:
+    def __init__(self, model, cache: SequenceCache, max_position: Optional[int] = None):
+        self.model = model
+        self.cache = cache
+        self.runtime = model.runtime
+        self.vocab_size = model.spec.vocab_size
+        self.max_position = max_position if max_position is not None else model.spec.max_position
+        self.builder = ContextBuilder(self.runtime.device)
+
+    # -- validation (host only; nothing has changed when it raises) ----------------------------
+    def _validate(self, slots, tokens, want) -> List[List[int]]:
+        if len(slots) != len(tokens):
+            raise StepError("one token list per slot is needed")
+        if len(set(slots)) != len(slots):
+            raise StepError("a slot appears twice in one step")
+        for s, t in zip(slots, tokens):
+            if not self.cache.table.in_use(s):
+                raise StepError(f"slot {s} is not in use")
+            if len(t) < 1:
+                raise StepError(f"slot {s} brings no token")
+            lo, hi = min(t), max(t)
+            if lo < 0 or hi >= self.vocab_size:
+                raise StepError(f"slot {s}: token id {lo if lo < 0 else hi} is outside the vocabulary [0, {self.vocab_size})")
+            end = self.cache.length(s) + len(t)
+            if end > self.max_position:
+                raise StepError(f"slot {s}: {end} positions exceed the model's limit of {self.max_position}")
+        if want == "last":
+            return [[len(t) - 1] for t in tokens]
+        if want == "all":
+            return [list(range(len(t))) for t in tokens]
+        if want is None:
+            return [[] for _ in tokens]
+        if len(want) != len(tokens):
+            raise StepError("one list of wanted places per slot is needed")
+        out = []
+        for s, t, w in zip(slots, tokens, want):
+            w = [int(x) for x in w]
+            if any(x < 0 or x >= len(t) for x in w):
+                raise StepError(f"slot {s}: a wanted place lies outside its {len(t)} tokens")
+            out.append(w)
+        return out
+
+    def prepare(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
+                want: Union[str, None, Sequence[Sequence[int]]] = "last",
+                into: Optional[torch.Tensor] = None, table_cols: Optional[int] = None) -> StepContext:
+        """Validates, reserves pages and uploads the step's description."""
+        want_lists = self._validate(slots, tokens, want)
+        n_new = [len(t) for t in tokens]
+        self.cache.reserve(slots, n_new)
+        start = [self.cache.length(s) for s in slots]
+        page = self.cache.page_size
+        cols = max(1, max(-(-(st + n) // page) for st, n in zip(start, n_new)))
+        if table_cols is not None:
+            if table_cols < cols:
+                raise StepError("the block table is narrower than the longest sequence")
+            cols = table_cols
+        tables = [self.cache.table.table_rows(g, slots, cols) for g in range(len(self.cache.kv_groups))]
+        return self.builder.build(slots, tokens, start, want_lists, tables, into=into)
+
+    def finish(self, ctx: StepContext) -> None:
+        self.cache.commit(ctx.host_slots, ctx.host_n_new)
+
+    def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
+             want: Union[str, None, Sequence[Sequence[int]]] = "last") -> Optional[torch.Tensor]:
+        """Runs the tokens and returns float32 logits [wanted, vocab] on the device (None if
+        nothing is wanted), rows in the order of the slots and of each slot's wanted places."""
+        ctx = self.prepare(slots, tokens, want)
+        logits = self.model.forward(ctx, self.cache)
+        self.finish(ctx)
+        return logits
+
+    def check_status(self) -> None:
+        """Reads the flag that kernels set when they meet an index out of range (this
+        waits for the device).  The kernels skip such an access; the results of that step
+        are not to be used."""
+        st = self.runtime.status
+        if st is not None:
+            v = int(st.item())
+            if v != 0:
+                st.zero_()
+                what = {1: "a token id outside the vocabulary", 2: "a cache write without a page",
+                        3: "a cache read without a page"}.get(v, f"code {v}")
+                raise CacheError(f"a kernel reported {what}")

@@ -1,0 +1,42 @@
+"""Gated feed-forward: g = Wg x, u = Wu x, h = act(g) * u, y = Wd h, added to the
+residual stream (src/model.cpp:1559-1565; silu(x) = x / (1 + exp(-x)), :1309).
+Gate and up are stacked into one product ([gate; up], the split the reference
+applies to a fused ``ffn_up``, src/model.cpp:1553-1557)."""
+from __future__ import annotations
+
+from typing import Dict, Mapping
+
+import torch
+
+from ..config.spec import PartSpec
+from ..csrc import ops
+from ..weights.loader import TensorReq
+from .base import Runtime, register_feed_forward
+from .linear import Linear
+
+
+class GatedMLP:
+    @classmethod
+    def manifest(cls, spec: PartSpec) -> Dict[str, TensorReq]:
+        d, ff = spec["hidden_size"], spec["intermediate_size"]
+        w = spec.weights
+        return {w["gate"]: TensorReq((ff, d)), w["up"]: TensorReq((ff, d)), w["down"]: TensorReq((d, ff))}
+
+    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
+        act = spec.get("activation", "silu")
+        if act != "silu":
+            raise ValueError(f"gated_mlp: activation {act!r} is not supported (silu)")
+        self.hidden = int(spec["hidden_size"])
+        self.intermediate = int(spec["intermediate_size"])
+        w = spec.weights
+        self.gate_up = Linear([tensors[w["gate"]], tensors[w["up"]]], runtime)
+        self.down = Linear([tensors[w["down"]]], runtime)
+        self.runtime = runtime
+
+    def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
+        gu = self.gate_up(x, out_dtype=torch.float32)
+        h = ops.swiglu(gu, self.runtime.act_dtype)
+        self.down(h, out=residual, accumulate=True)
+
+
+register_feed_forward("gated_mlp", GatedMLP)
