@@ -1,13 +1,102 @@
-"""Attention kernels for the bfloat16 path: which kernel takes which shape."""
+"""Attention kernels of the bfloat16 path: one compiled module per head size.
+
+``attention_bf16.cu`` is specialised at compile time for a head size and for the number
+of query heads a decode block serves; the module for the sizes a model has is compiled
+the first time that model runs a step (a few seconds) and kept beside the core library.
+"""
 from __future__ import annotations
 
-from typing import Optional
+import ctypes
+from typing import Dict, Optional, Tuple
 
 import torch
+
+from . import build
+from .ops import KernelError, _check, _ptr, _stream
+
+_vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_modules: Dict[Tuple[int, int], ctypes.CDLL] = {}
+
+DECODE_CHUNK_PAGES = 4        # a decode block covers 4 pages = 256 keys; chunks start at multiples of that
+
+
+def lanes_per_key(head_dim: int) -> int:
+    for l in (16, 8, 4, 2, 1):
+        if head_dim % (8 * l) == 0 and head_dim // l <= 32:
+            return l
+    for l in (16, 8, 4, 2, 1):
+        if head_dim % (8 * l) == 0:
+            return l
+    return 1
+
+
+def heads_per_block(head_dim: int, group: int) -> int:
+    dpl = head_dim // lanes_per_key(head_dim)
+    cap = 4 if dpl <= 16 else 2 if dpl <= 32 else 1
+    return max(1, min(group, cap))
+
+
+def supported(head_dim: int) -> bool:
+    return head_dim % 16 == 0 and 16 <= head_dim <= 256
+
+
+def module(head_dim: int, gc: int) -> ctypes.CDLL:
+    key = (head_dim, gc)
+    m = _modules.get(key)
+    if m is None:
+        m = build.load_library(f"ithaca_attn_hd{head_dim}_g{gc}", ["attention_bf16.cu"],
+                               defines=[f"IK_HD={head_dim}", f"IK_GC={gc}"])
+        m.ik_attn_prefill.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp]
+        m.ik_attn_prefill.restype = _i
+        m.ik_attn_decode.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _i, _i, _i,
+                                     _vp, _vp]
+        m.ik_attn_decode.restype = _i
+        if m.ik_attn_head_dim() != head_dim:
+            raise KernelError("the attention module was compiled for another head size")
+        _modules[key] = m
+    return m
+
+
+def prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, cu_seqlens: torch.Tensor,
+            kv_lens: torch.Tensor, table: torch.Tensor, n_seqs: int, max_new: int, n_heads: int, scale: float,
+            window: int, status: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    n_pages, nkv, page_size, hd = k_pages.shape
+    m = module(hd, heads_per_block(hd, n_heads // nkv))
+    if out is None:
+        out = torch.empty_like(q)
+    _check(m.ik_attn_prefill(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(cu_seqlens), _ptr(kv_lens),
+                             _ptr(table), table.stride(0), n_seqs, max_new, n_heads, nkv, scale, window, page_size,
+                             n_pages, _ptr(status), _stream()), "attention prefill")
+    return out
+
+
+def decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, kv_lens: torch.Tensor, table: torch.Tensor,
+           n_seqs: int, kv_len_bound: int, n_heads: int, scale: float, window: int, status: Optional[torch.Tensor],
+           out: Optional[torch.Tensor] = None, chunk_pages: int = DECODE_CHUNK_PAGES) -> torch.Tensor:
+    """``kv_len_bound``: no sequence of the step is longer than this (it sizes the grid and the
+    scratch for the partial results; blocks beyond a sequence's length return at once)."""
+    n_pages, nkv, page_size, hd = k_pages.shape
+    m = module(hd, heads_per_block(hd, n_heads // nkv))
+    n_splits = max(1, -(-kv_len_bound // (chunk_pages * page_size)))
+    part_o = torch.empty((n_seqs, n_heads, n_splits, hd), dtype=torch.float32, device=q.device)
+    part_ml = torch.empty((n_seqs, n_heads, n_splits, 2), dtype=torch.float32, device=q.device)
+    if out is None:
+        out = torch.empty_like(q)
+    _check(m.ik_attn_decode(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(part_o), _ptr(part_ml),
+                            _ptr(kv_lens), _ptr(table), table.stride(0), n_seqs, n_heads, nkv, scale, window,
+                            page_size, n_pages, chunk_pages, n_splits, _ptr(status), _stream()), "attention decode")
+    return out
 
 
 def attend(q, k_pages, v_pages, ctx, table, n_heads: int, scale: float, window: int,
            status) -> Optional[torch.Tensor]:
     """Returns None when no specialised kernel takes these sizes (the caller then uses the
     CUDA-core kernel)."""
-    return None
+    n_pages, nkv, page_size, hd = k_pages.shape
+    if k_pages.dtype != torch.bfloat16 or q.dtype != torch.bfloat16 or page_size != 64 or not supported(hd):
+        return None
+    if ctx.is_decode:
+        return decode(q, k_pages, v_pages, ctx.kv_lens, table, ctx.n_seqs, ctx.kv_len_bound, n_heads, scale, window,
+                      status)
+    return prefill(q, k_pages, v_pages, ctx.cu_seqlens, ctx.kv_lens, table, ctx.n_seqs, ctx.max_new, n_heads, scale,
+                   window, status)

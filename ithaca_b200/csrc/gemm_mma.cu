@@ -1,0 +1,273 @@
+// bfloat16 products on the warp-level tensor-core path (mma.sync m16n8k16, float accumulate):
+//   Y[M, N] (+)= X[M, K] * W[N, K]^T,  X and W bfloat16 with rows contiguous, Y float or bfloat16.
+//
+// Two kernels.
+//  * skinny (M <= 64, decode): weights are the 16-row operand, tokens the 8-column operand, so a
+//    handful of tokens costs no wasted tensor work.  A block owns 16 or 32 weight rows; its 8
+//    warps split K between them and their partial sums are added in warp order at the end.
+//    Each thread streams 16 contiguous bytes of a weight row per load, straight from global
+//    memory to registers: weights are read exactly once.
+//  * tiled (any M, prefill): 128 x 128 x 32 tiles through shared memory with a 4-stage
+//    cp.async pipeline.
+//
+// Both feed the MMA without ldmatrix: a thread's 16 bytes (8 consecutive k) serve as the
+// fragments of two MMAs, with the same permutation of k applied to both operands (a dot
+// product does not care in which order its terms are paired, as long as both sides agree).
+//
+// The order in which a result's K terms are added depends on K alone (and on which of the
+// two kernels runs), never on M or N.  Needs K % 8 == 0 and 16-byte aligned rows; the entry
+// points return IK_UNSUPPORTED otherwise and the caller uses the CUDA-core product.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {      // read-once data: do not keep it in L1
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void store_out(float* Y, size_t o, float v, int accumulate) {
+    Y[o] = accumulate ? Y[o] + v : v;
+}
+__device__ __forceinline__ void store_out(__nv_bfloat16* Y, size_t o, float v, int accumulate) {
+    Y[o] = __float2bfloat16_rn(accumulate ? __bfloat162float(Y[o]) + v : v);
+}
+
+// ------------------------------------------------------------------------------------------ skinny
+// NT: 8-token column tiles (M <= 8 NT).  RF: 16-row fragments per block (R = 16 RF rows).
+template <int NT, int RF, typename TY>
+__global__ void __launch_bounds__(256)
+gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, TY* __restrict__ Y,
+                   int M, int N, int K, int ldx, int ldw, int ldy, int accumulate) {
+    constexpr int R = 16 * RF, COLS = 8 * NT;
+    extern __shared__ float red[];                       // [8 warps][R][COLS]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * R;
+
+    float acc[RF][NT][4];
+    #pragma unroll
+    for (int r = 0; r < RF; r++)
+        #pragma unroll
+        for (int n = 0; n < NT; n++)
+            #pragma unroll
+            for (int i = 0; i < 4; i++) acc[r][n][i] = 0.f;
+
+    const __nv_bfloat16* wrow[RF][2];
+    bool wok[RF][2];
+    #pragma unroll
+    for (int r = 0; r < RF; r++)
+        #pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int row = n0 + r * 16 + h * 8 + g;
+            wok[r][h] = row < N;
+            wrow[r][h] = W + (size_t)(wok[r][h] ? row : 0) * ldw;
+        }
+    const __nv_bfloat16* xrow[NT];
+    bool xok[NT];
+    #pragma unroll
+    for (int n = 0; n < NT; n++) {
+        const int m = n * 8 + g;
+        xok[n] = m < M;
+        xrow[n] = X + (size_t)(xok[n] ? m : 0) * ldx;
+    }
+
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    const int nblk = (K + 63) / 64;                       // blocks of 64 k = two 32-k chunks, 128 bytes of a row
+    for (int blk = warp; blk < nblk; blk += 8) {
+        uint4 a[2][RF][2], b[2][NT];
+        #pragma unroll
+        for (int c = 0; c < 2; c++) {
+            const int k = blk * 64 + c * 32 + t * 8;
+            const bool kok = k < K;                       // K % 8 == 0: the whole 8 are inside
+            #pragma unroll
+            for (int r = 0; r < RF; r++)
+                #pragma unroll
+                for (int h = 0; h < 2; h++) a[c][r][h] = (kok && wok[r][h]) ? ld_stream(wrow[r][h] + k) : zero;
+            #pragma unroll
+            for (int n = 0; n < NT; n++) b[c][n] = (kok && xok[n]) ? __ldg((const uint4*)(xrow[n] + k)) : zero;
+        }
+        #pragma unroll
+        for (int c = 0; c < 2; c++)
+            #pragma unroll
+            for (int r = 0; r < RF; r++)
+                #pragma unroll
+                for (int n = 0; n < NT; n++) {
+                    mma_bf16(acc[r][n], a[c][r][0].x, a[c][r][1].x, a[c][r][0].y, a[c][r][1].y, b[c][n].x, b[c][n].y);
+                    mma_bf16(acc[r][n], a[c][r][0].z, a[c][r][1].z, a[c][r][0].w, a[c][r][1].w, b[c][n].z, b[c][n].w);
+                }
+    }
+    // partial sums of the 8 warps, added in warp order
+    float* mine = red + (size_t)warp * R * COLS;
+    #pragma unroll
+    for (int r = 0; r < RF; r++)
+        #pragma unroll
+        for (int n = 0; n < NT; n++) {
+            const int row = r * 16 + g, col = n * 8 + 2 * t;
+            mine[(row) * COLS + col] = acc[r][n][0];
+            mine[(row) * COLS + col + 1] = acc[r][n][1];
+            mine[(row + 8) * COLS + col] = acc[r][n][2];
+            mine[(row + 8) * COLS + col + 1] = acc[r][n][3];
+        }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < R * COLS; idx += 256) {
+        const int m = idx / R, row = idx % R;             // consecutive threads: consecutive features
+        if (m >= M || n0 + row >= N) continue;
+        float s = 0.f;
+        #pragma unroll
+        for (int w = 0; w < 8; w++) s += red[(size_t)w * R * COLS + row * COLS + m];
+        store_out(Y, (size_t)m * ldy + n0 + row, s, accumulate);
+    }
+}
+
+template <int NT, int RF, typename TY>
+int launch_skinny(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
+                  int accumulate, cudaStream_t stream) {
+    constexpr int R = 16 * RF;
+    const size_t smem = (size_t)8 * R * 8 * NT * sizeof(float);
+    auto kern = gemm_skinny_kernel<NT, RF, TY>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    kern<<<(N + R - 1) / R, 256, smem, stream>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (TY*)Y, M, N, K, ldx,
+                                                  ldw, ldy, accumulate);
+    IK_LAUNCH_STATUS();
+}
+
+// ------------------------------------------------------------------------------------------ tiled
+constexpr int TBM = 128, TBN = 128, TBK = 32, STAGES = 4;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    const int n = valid ? 16 : 0;                         // 0 source bytes: the 16 destination bytes become zero
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" :: "r"(s), "l"(gmem), "r"(n));
+}
+
+template <typename TY>
+__global__ void __launch_bounds__(256)
+gemm_tiled_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, TY* __restrict__ Y,
+                  int M, int N, int K, int ldx, int ldw, int ldy, int accumulate) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* xs = (__nv_bfloat16*)smem_raw;                         // [STAGES][TBM][TBK]
+    __nv_bfloat16* ws = xs + (size_t)STAGES * TBM * TBK;                  // [STAGES][TBN][TBK]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int wm = warp >> 2, wn = warp & 3;                              // 2 x 4 warps, each 64 tokens x 32 features
+    const int m0 = blockIdx.y * TBM, n0 = blockIdx.x * TBN;
+    const int nk = (K + TBK - 1) / TBK;
+
+    auto load_stage = [&](int stage, int kt) {
+        const int k0 = kt * TBK;
+        #pragma unroll
+        for (int l = 0; l < 2; l++) {
+            const int idx = threadIdx.x + l * 256;                        // 512 chunks of 16 bytes per operand
+            const int row = idx >> 2, ch = idx & 3;
+            const int k = k0 + ch * 8;
+            const bool kok = kt < nk && k < K;
+            const bool xv = kok && (m0 + row) < M, wv = kok && (n0 + row) < N;
+            cp_async16(xs + ((size_t)stage * TBM + row) * TBK + ch * 8, xv ? X + (size_t)(m0 + row) * ldx + k : X, xv);
+            cp_async16(ws + ((size_t)stage * TBN + row) * TBK + ch * 8, wv ? W + (size_t)(n0 + row) * ldw + k : W, wv);
+        }
+        asm volatile("cp.async.commit_group;\n");
+    };
+
+    float acc[4][4][4];
+    #pragma unroll
+    for (int i = 0; i < 4; i++)
+        #pragma unroll
+        for (int j = 0; j < 4; j++)
+            #pragma unroll
+            for (int e = 0; e < 4; e++) acc[i][j][e] = 0.f;
+
+    for (int s = 0; s < STAGES - 1; s++) load_stage(s, s);
+    for (int kt = 0; kt < nk; kt++) {
+        asm volatile("cp.async.wait_group %0;\n" :: "n"(STAGES - 2));
+        __syncthreads();
+        load_stage((kt + STAGES - 1) % STAGES, kt + STAGES - 1);          // refills the stage read at kt - 1
+        const int st = kt % STAGES;
+        const __nv_bfloat16* xa = xs + ((size_t)st * TBM + wm * 64) * TBK;
+        const __nv_bfloat16* wb = ws + ((size_t)st * TBN + wn * 32) * TBK;
+        uint4 a[4][2], b[4];
+        #pragma unroll
+        for (int i = 0; i < 4; i++) {
+            a[i][0] = *(const uint4*)(xa + (i * 16 + g) * TBK + t * 8);
+            a[i][1] = *(const uint4*)(xa + (i * 16 + g + 8) * TBK + t * 8);
+        }
+        #pragma unroll
+        for (int j = 0; j < 4; j++) b[j] = *(const uint4*)(wb + (j * 8 + g) * TBK + t * 8);
+        #pragma unroll
+        for (int i = 0; i < 4; i++)
+            #pragma unroll
+            for (int j = 0; j < 4; j++) {
+                mma_bf16(acc[i][j], a[i][0].x, a[i][1].x, a[i][0].y, a[i][1].y, b[j].x, b[j].y);
+                mma_bf16(acc[i][j], a[i][0].z, a[i][1].z, a[i][0].w, a[i][1].w, b[j].z, b[j].w);
+            }
+    }
+    asm volatile("cp.async.wait_group 0;\n");
+    #pragma unroll
+    for (int i = 0; i < 4; i++)
+        #pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + wn * 32 + j * 8 + 2 * t;
+            #pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int m = m0 + wm * 64 + i * 16 + g + h * 8;
+                if (m >= M) continue;
+                if (n < N) store_out(Y, (size_t)m * ldy + n, acc[i][j][2 * h], accumulate);
+                if (n + 1 < N) store_out(Y, (size_t)m * ldy + n + 1, acc[i][j][2 * h + 1], accumulate);
+            }
+        }
+}
+
+template <typename TY>
+int launch_tiled(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy, int accumulate,
+                 cudaStream_t stream) {
+    const size_t smem = (size_t)STAGES * (TBM + TBN) * TBK * sizeof(__nv_bfloat16);
+    auto kern = gemm_tiled_kernel<TY>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid((N + TBN - 1) / TBN, (M + TBM - 1) / TBM);
+    kern<<<grid, 256, smem, stream>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (TY*)Y, M, N, K, ldx, ldw, ldy,
+                                      accumulate);
+    IK_LAUNCH_STATUS();
+}
+
+bool aligned_ok(const void* X, const void* W, int K, int ldx, int ldw) {
+    return K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)X % 16) == 0 && ((uintptr_t)W % 16) == 0;
+}
+
+}  // namespace
+
+// kind: 0 = choose by M (skinny for M <= 64, else tiled), 1 = skinny, 2 = tiled.
+IK_EXPORT int ik_gemm_bf16_mma(const void* X, const void* W, void* Y, int y_dtype, int M, int N, int K, int ldx, int ldw,
+                               int ldy, int accumulate, int kind, cudaStream_t stream) {
+    if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || ldy < N) return IK_BAD_ARGUMENT;
+    if (y_dtype != IK_F32 && y_dtype != IK_BF16) return IK_BAD_ARGUMENT;
+    if (!aligned_ok(X, W, K, ldx, ldw)) return IK_UNSUPPORTED;
+    if (M == 0) return IK_OK;
+    const bool skinny = kind == 1 || (kind == 0 && M <= 64);
+    if (skinny && M > 64) return IK_UNSUPPORTED;
+#define IK_SK(NT, RF)                                                                                          \
+    return y_dtype == IK_F32 ? launch_skinny<NT, RF, float>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, stream) \
+                             : launch_skinny<NT, RF, __nv_bfloat16>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, stream)
+    if (skinny) {
+        // 32 rows a block when that still gives every SM two blocks, else 16 rows a block
+        const bool wide = (N + 31) / 32 >= 2 * 148;
+        if (M <= 8) { if (wide) { IK_SK(1, 2); } IK_SK(1, 1); }
+        if (M <= 16) { if (wide) { IK_SK(2, 2); } IK_SK(2, 1); }
+        if (M <= 32) { if (wide) { IK_SK(4, 2); } IK_SK(4, 1); }
+        IK_SK(8, 1);
+    }
+#undef IK_SK
+    return y_dtype == IK_F32 ? launch_tiled<float>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, stream)
+                             : launch_tiled<__nv_bfloat16>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, stream);
+}

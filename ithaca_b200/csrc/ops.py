@@ -62,6 +62,7 @@ _SIGNATURES = {
     "ik_swiglu": [_vp, _vp, _i, _i, _i, _vp],
     "ik_rope_append": [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "ik_gemm_bf16_mma": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "ik_attention_simt": [_vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp],
     "ik_argmax": [_vp, _i, _vp, _i, _i, _vp],
     "ik_sample": [_vp, _i, _vp, _vp, _i, _i, _f, _i, _f, _f, _vp, _i, _u64, _vp, _vp, _vp],
@@ -164,6 +165,32 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         raise KernelError("gemm: the output has the wrong shape")
     _check(lib().ik_gemm_simt(_ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), M, N, K, x.stride(0),
                               w.stride(0), out.stride(0), 1 if accumulate else 0, _stream()), "gemm_simt")
+    return out
+
+
+def gemm_bf16_mma(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=torch.float32,
+                  accumulate: bool = False, kind: int = 0) -> Optional[torch.Tensor]:
+    """bfloat16 operands, float accumulation on the warp-level tensor-core path.  ``kind``: 0 = by
+    M, 1 = the skinny (decode) kernel, 2 = the tiled kernel.  Returns None when the kernels
+    do not take these sizes (K not a multiple of 8, unaligned rows)."""
+    _need(x, "x", torch.bfloat16, contiguous=False)
+    _need(w, "w", torch.bfloat16, contiguous=False)
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2 or x.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError(f"gemm: shapes {tuple(x.shape)} x {tuple(w.shape)}^T do not match or rows are not contiguous")
+    if out is None:
+        if accumulate:
+            raise KernelError("gemm: accumulate needs an output to add to")
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _need(out, "out", contiguous=False)
+    if out.shape != (M, N) or out.stride(1) != 1:
+        raise KernelError("gemm: the output has the wrong shape")
+    st = lib().ik_gemm_bf16_mma(_ptr(x), _ptr(w), _ptr(out), _code(out), M, N, K, x.stride(0), w.stride(0),
+                                out.stride(0), 1 if accumulate else 0, kind, _stream())
+    if st == -2:
+        return None
+    _check(st, "gemm_bf16_mma")
     return out
 
 

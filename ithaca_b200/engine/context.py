@@ -30,6 +30,7 @@ class StepContext:
     is_decode: bool                    # every sequence brings exactly one token
     max_new: int
     max_kv_len: int
+    kv_len_bound: int = 0              # no sequence is longer than this (sizes grids; >= max_kv_len)
     host_slots: List[int] = field(default_factory=list)
     host_n_new: List[int] = field(default_factory=list)
     host_kv_lens: List[int] = field(default_factory=list)
@@ -94,5 +95,5 @@ class ContextBuilder:
             n_tokens=T, n_seqs=B, n_logit_rows=int(rows.size), token_ids=view(0), token_seq=view(1),
             token_pos=view(2), cu_seqlens=view(3), slots=view(4), kv_lens=view(5), logit_rows=view(6), tables=tabs,
             is_decode=all(n == 1 for n in n_new), max_new=max(n_new) if n_new else 0,
-            max_kv_len=int(kv_lens.max()) if B else 0, host_slots=list(slots), host_n_new=n_new,
+            max_kv_len=int(kv_lens.max()) if B else 0, kv_len_bound=int(kv_lens.max()) if B else 0, host_slots=list(slots), host_n_new=n_new,
             host_kv_lens=[int(x) for x in kv_lens])

@@ -1,0 +1,333 @@
+"""Each kernel alone against a plain float64 reference of the same operation, at sizes other
+than the engine's tiny models use, including ragged ones."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain import llama_plain as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops():
+    from ithaca_b200.csrc import ops as o
+    return o
+
+
+def close(got, ref, rel):
+    got = got.detach().double().cpu()
+    ref = ref.detach().double().cpu()
+    assert got.shape == ref.shape
+    assert torch.isfinite(got).all()
+    err = (got - ref).abs().max().item() / max(ref.abs().max().item(), 1e-30)
+    assert err <= rel, f"relative error {err:.3e} > {rel:.1e}"
+
+
+def rnd(shape, seed, dtype=torch.float32, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+# ------------------------------------------------------------------------------------------ simple kernels
+@pytest.mark.parametrize("table_dtype", [torch.float32, torch.bfloat16])
+def test_embed(table_dtype):
+    table = rnd((301, 72), 0, table_dtype)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = ops().embed(ids.to(DEV), table.to(DEV), 1.5, status)
+    close(out, table.double()[ids.long()] * 1.5, 1e-7)
+    assert status.item() == 0
+    bad = torch.tensor([3, 301], dtype=torch.int32, device=DEV)
+    out = ops().embed(bad, table.to(DEV), 1.0, status)
+    assert status.item() == 1 and out[1].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("d", [64, 200, 4096, 5000])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm(d, out_dtype):
+    x = rnd((7, d), 1, scale=3.0)
+    w = 1 + rnd((d,), 2, scale=0.1)
+    got = ops().rmsnorm(x.to(DEV), w.to(DEV), 1e-5, out_dtype)
+    ref = P.rmsnorm(x.double(), w.double(), 1e-5)
+    close(got, ref, 2e-6 if out_dtype == torch.float32 else 5e-3)
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    got = ops().rmsnorm(x.to(DEV), w.to(DEV), 1e-5, out_dtype, rows_in=rows)
+    close(got, ref[[6, 0, 3]], 2e-6 if out_dtype == torch.float32 else 5e-3)
+
+
+@pytest.mark.parametrize("ff", [172, 512, 1000])
+def test_swiglu(ff):
+    gu = rnd((9, 2 * ff), 3, scale=2.0)
+    ref = P.silu(gu[:, :ff].double()) * gu[:, ff:].double()
+    close(ops().swiglu(gu.to(DEV), torch.float32), ref, 2e-6)
+    close(ops().swiglu(gu.to(DEV), torch.bfloat16), ref, 5e-3)
+
+
+# ------------------------------------------------------------------------------------------ products
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (5, 172, 64), (33, 70, 172), (130, 257, 300), (64, 384, 192)])
+@pytest.mark.parametrize("wdt", [torch.float32, torch.bfloat16])
+def test_gemm_simt_float32(M, N, K, wdt):
+    x, w = rnd((M, K), 4), rnd((N, K), 5, wdt)
+    ref = x.double() @ w.double().T
+    got = ops().gemm_simt(x.to(DEV), w.to(DEV))
+    close(got, ref, 2e-6)
+    base = rnd((M, N), 6)
+    got = ops().gemm_simt(x.to(DEV), w.to(DEV), out=base.to(DEV), accumulate=True)
+    close(got, ref + base.double(), 2e-6)
+
+
+def test_gemm_simt_rows_do_not_depend_on_batch():
+    """A row's result is the same bits whether it is computed alone or among others."""
+    x, w = rnd((37, 300), 7), rnd((129, 300), 8)
+    full = ops().gemm_simt(x.to(DEV), w.to(DEV))
+    for r in (0, 5, 36):
+        one = ops().gemm_simt(x[r:r + 1].to(DEV), w.to(DEV))
+        assert torch.equal(one[0], full[r])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (8, 200, 72), (9, 4096, 512), (16, 130, 1024), (31, 96, 264),
+                                   (64, 300, 2048), (3, 40, 8)])
+@pytest.mark.parametrize("kind", [1, 2])
+@pytest.mark.parametrize("ydt", [torch.float32, torch.bfloat16])
+def test_gemm_bf16_mma(M, N, K, kind, ydt):
+    x, w = rnd((M, K), 9, torch.bfloat16), rnd((N, K), 10, torch.bfloat16)
+    ref = x.double() @ w.double().T
+    got = ops().gemm_bf16_mma(x.to(DEV), w.to(DEV), out_dtype=ydt, kind=kind)
+    assert got is not None
+    close(got, ref, 2e-5 if ydt == torch.float32 else 5e-3)
+    base = rnd((M, N), 11, ydt)
+    got = ops().gemm_bf16_mma(x.to(DEV), w.to(DEV), out=base.to(DEV).clone(), accumulate=True, kind=kind)
+    close(got, ref + base.double(), 2e-5 if ydt == torch.float32 else 8e-3)
+
+
+@pytest.mark.parametrize("M,N,K", [(200, 500, 328), (129, 128, 4096), (1000, 260, 72)])
+def test_gemm_bf16_tiled_large(M, N, K):
+    x, w = rnd((M, K), 12, torch.bfloat16), rnd((N, K), 13, torch.bfloat16)
+    got = ops().gemm_bf16_mma(x.to(DEV), w.to(DEV), kind=2)
+    close(got, x.double() @ w.double().T, 2e-5)
+
+
+def test_gemm_bf16_refuses_unaligned_k():
+    x, w = rnd((4, 172), 14, torch.bfloat16), rnd((64, 172), 15, torch.bfloat16)
+    assert ops().gemm_bf16_mma(x.to(DEV), w.to(DEV)) is None           # K % 8 != 0
+    from ithaca_b200.csrc import gemm_bf16
+    close(gemm_bf16.gemm(x.to(DEV), w.to(DEV)), x.double() @ w.double().T, 2e-5)   # the dispatcher falls back
+
+
+# ------------------------------------------------------------------------------------------ rotary + cache
+class Paged:
+    """Sequences laid into pages in a scrambled order, the way a used cache looks."""
+
+    def __init__(self, lens, nkv, hd, dtype, seed, page=64, spare=3):
+        self.page, self.nkv, self.hd = page, nkv, hd
+        need = sum(-(-l // page) for l in lens)
+        self.n_pages = need + spare
+        perm = np.random.default_rng(seed).permutation(self.n_pages)[:need]
+        cols = max(-(-l // page) for l in lens)
+        self.table = np.full((len(lens), cols), -1, dtype=np.int32)
+        it = iter(perm)
+        for b, l in enumerate(lens):
+            for c in range(-(-l // page)):
+                self.table[b, c] = next(it)
+        self.k = torch.zeros((self.n_pages, nkv, page, hd), dtype=dtype)
+        self.v = torch.zeros_like(self.k)
+        self.lens = list(lens)
+
+    def fill(self, ks, vs):
+        for b, (k, v) in enumerate(zip(ks, vs)):
+            for j in range(k.shape[0]):
+                pg = self.table[b, j // self.page]
+                self.k[pg, :, j % self.page] = k[j].to(self.k.dtype)
+                self.v[pg, :, j % self.page] = v[j].to(self.v.dtype)
+
+    def dev(self):
+        return self.k.to(DEV), self.v.to(DEV), torch.from_numpy(self.table).to(DEV)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,rot,pairing", [(4, 4, 16, 16, 0), (6, 2, 32, 32, 1), (5, 1, 48, 32, 0)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_append(nh, nkv, hd, rot, pairing, dtype):
+    lens, new = [70, 5, 130], [3, 5, 66]                    # sequence lengths after the step, tokens it brings
+    T = sum(new)
+    qkv = rnd((T, (nh + 2 * nkv) * hd), 20)
+    inv = P.rope_inv_freq(rot, 10000.0, None)
+    pg = Paged(lens, nkv, hd, dtype, seed=1)
+    token_seq = np.repeat(np.arange(3), new).astype(np.int32)
+    token_pos = np.concatenate([np.arange(l - n, l) for l, n in zip(lens, new)]).astype(np.int32)
+    k_d, v_d, tab = pg.dev()
+    q_out = torch.empty((T, nh * hd), dtype=dtype, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().rope_append(qkv.to(DEV), q_out, k_d, v_d, torch.from_numpy(token_seq).to(DEV),
+                      torch.from_numpy(token_pos).to(DEV), tab, inv.to(DEV), nh, nkv, hd, rot, pairing, True, status)
+    assert status.item() == 0
+    x = qkv.double().view(T, nh + 2 * nkv, hd)
+    pos = torch.from_numpy(token_pos)
+    name = "half" if pairing == 0 else "interleaved"
+    q_ref = P.rope(x[:, :nh], pos, inv, name)
+    k_ref = P.rope(x[:, nh:nh + nkv], pos, inv, name)
+    v_ref = x[:, nh + nkv:]
+    tol = 2e-6 if dtype == torch.float32 else 5e-3
+    close(q_out.view(T, nh, hd), q_ref, tol)
+    k_h, v_h = k_d.cpu(), v_d.cpu()
+    got_k = torch.stack([k_h[pg.table[s, p // 64], :, p % 64] for s, p in zip(token_seq, token_pos)])
+    got_v = torch.stack([v_h[pg.table[s, p // 64], :, p % 64] for s, p in zip(token_seq, token_pos)])
+    close(got_k, k_ref, tol)
+    close(got_v, v_ref, tol)
+    # nothing else in the pool was touched
+    touched = torch.zeros(k_h.shape[0], 64, dtype=torch.bool)
+    for s, p in zip(token_seq, token_pos):
+        touched[pg.table[s, p // 64], p % 64] = True
+    assert k_h.float().abs().sum(dim=(1, 3))[~touched].max().item() == 0
+
+
+# ------------------------------------------------------------------------------------------ attention
+def attention_case(nh, nkv, hd, lens, new, window, dtype, seed, boost=None):
+    """Random q/k/v for sequences of the given lengths, the last ``new[b]`` tokens of each being
+    this step's queries.  Returns everything the kernels need plus the plain result."""
+    g = torch.Generator().manual_seed(seed)
+    ks = [torch.randn((l, nkv, hd), generator=g) for l in lens]
+    vs = [torch.randn((l, nkv, hd), generator=g) for l in lens]
+    qs = [torch.randn((l, nh, hd), generator=g) for l in lens]
+    if boost is not None:
+        boost(qs, ks, vs)
+    ks = [k.to(dtype) for k in ks]
+    vs = [v.to(dtype) for v in vs]
+    qs = [q.to(dtype) for q in qs]
+    pg = Paged(lens, nkv, hd, dtype, seed)
+    pg.fill(ks, vs)
+    ref = torch.cat([P.attention(q.double(), k.double(), v.double(), window=window)[l - n:]
+                     for q, k, v, l, n in zip(qs, ks, vs, lens, new)])
+    q_step = torch.cat([q[l - n:] for q, l, n in zip(qs, lens, new)]).reshape(sum(new), nh * hd)
+    token_seq = np.repeat(np.arange(len(lens)), new).astype(np.int32)
+    token_pos = np.concatenate([np.arange(l - n, l) for l, n in zip(lens, new)]).astype(np.int32)
+    cu = np.concatenate([[0], np.cumsum(new)]).astype(np.int32)
+    return dict(q=q_step.to(DEV), pg=pg, ref=ref.reshape(sum(new), nh * hd), token_seq=torch.from_numpy(token_seq).to(DEV),
+                token_pos=torch.from_numpy(token_pos).to(DEV), cu=torch.from_numpy(cu).to(DEV),
+                kv_lens=torch.tensor(lens, dtype=torch.int32, device=DEV))
+
+
+SHAPES = [(4, 4, 16), (6, 2, 32), (5, 1, 48), (8, 2, 64), (8, 4, 128)]
+
+
+@pytest.mark.parametrize("nh,nkv,hd", SHAPES)
+@pytest.mark.parametrize("window", [0, 40])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_simt(nh, nkv, hd, window, dtype):
+    lens, new = [1, 70, 200, 129], [1, 70, 3, 1]
+    c = attention_case(nh, nkv, hd, lens, new, window or None, dtype, seed=30)
+    k_d, v_d, tab = c["pg"].dev()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    got = ops().attention_simt(c["q"], k_d, v_d, c["token_seq"], c["token_pos"], tab, nh, 1 / math.sqrt(hd), window,
+                               status)
+    assert status.item() == 0
+    close(got, c["ref"], 3e-6 if dtype == torch.float32 else 8e-3)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", SHAPES)
+@pytest.mark.parametrize("window", [0, 40, 100])
+def test_attention_bf16_prefill(nh, nkv, hd, window):
+    from ithaca_b200.csrc import attention_bf16 as A
+    lens, new = [1, 70, 200, 129, 64], [1, 70, 67, 129, 5]       # whole prompts and later chunks
+    c = attention_case(nh, nkv, hd, lens, new, window or None, torch.bfloat16, seed=31)
+    k_d, v_d, tab = c["pg"].dev()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    got = A.prefill(c["q"], k_d, v_d, c["cu"], c["kv_lens"], tab, len(lens), max(new), nh, 1 / math.sqrt(hd), window,
+                    status)
+    assert status.item() == 0
+    close(got, c["ref"], 8e-3)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", SHAPES)
+@pytest.mark.parametrize("window", [0, 40, 300])
+def test_attention_bf16_decode(nh, nkv, hd, window):
+    from ithaca_b200.csrc import attention_bf16 as A
+    lens = [1, 64, 65, 257, 700, 1030]
+    new = [1] * len(lens)
+    c = attention_case(nh, nkv, hd, lens, new, window or None, torch.bfloat16, seed=32)
+    k_d, v_d, tab = c["pg"].dev()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for bound in (max(lens), 2048):                                     # a larger grid must not change anything
+        got = A.decode(c["q"], k_d, v_d, c["kv_lens"], tab, len(lens), bound, nh, 1 / math.sqrt(hd), window, status)
+        assert status.item() == 0
+        close(got, c["ref"], 8e-3)
+
+
+@pytest.mark.parametrize("kind", ["simt32", "prefill", "decode"])
+def test_attention_reaches_a_far_key_and_respects_the_window_edge(kind):
+    """One key far back is made to dominate the last query's scores: the output must be that
+    key's value.  Under a window the same key just outside must not count, just inside must."""
+    from ithaca_b200.csrc import attention_bf16 as A
+    nh, nkv, hd, L = 4, 2, 64, 700
+    dtype = torch.float32 if kind == "simt32" else torch.bfloat16
+    for window, far in [(0, 3), (0, 130), (100, L - 100), (100, L - 101)]:
+        def boost(qs, ks, vs, far=far):
+            d = torch.zeros(hd)
+            d[0] = 1.0
+            qs[0][L - 1] = d * 40.0
+            ks[0][:] *= 0.05
+            ks[0][far] = d * 40.0
+        n_new = 1 if kind == "decode" else 5
+        c = attention_case(nh, nkv, hd, [L], [n_new], window or None, dtype, seed=33, boost=boost)
+        k_d, v_d, tab = c["pg"].dev()
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        scale = 1 / math.sqrt(hd)
+        if kind == "simt32":
+            got = ops().attention_simt(c["q"], k_d, v_d, c["token_seq"], c["token_pos"], tab, nh, scale, window, status)
+        elif kind == "prefill":
+            got = A.prefill(c["q"], k_d, v_d, c["cu"], c["kv_lens"], tab, 1, n_new, nh, scale, window, status)
+        else:
+            got = A.decode(c["q"], k_d, v_d, c["kv_lens"], tab, 1, L, nh, scale, window, status)
+        close(got, c["ref"], 3e-6 if dtype == torch.float32 else 8e-3)
+        # the construction does what it says: inside the reach the far value is the output
+        pgt = c["pg"]
+        far_v = pgt.v[pgt.table[0, far // 64], :, far % 64].double()          # [nkv, hd]
+        last = got[-1].double().cpu().view(nh, hd)
+        inside = window == 0 or far > L - 1 - window
+        hit = (last - far_v.repeat_interleave(nh // nkv, 0)).abs().max().item() < 0.05
+        assert hit == inside
+
+
+# ------------------------------------------------------------------------------------------ sampling
+def test_argmax_takes_the_first_of_equal_maxima():
+    lg = rnd((5, 3001), 40)
+    lg[2, 77] = lg[2, 2500] = 9.0
+    got = ops().argmax(lg.to(DEV)).cpu()
+    assert got.tolist() == [int(torch.argmax(r)) for r in lg[:2]] + [77] + [int(torch.argmax(r)) for r in lg[3:]]
+
+
+@pytest.mark.parametrize("V", [256, 384, 5003])
+@pytest.mark.parametrize("temp,top_k,top_p,pen", [(0.8, 40, 0.9, 1.1), (1.0, 5, 1.0, 1.0), (0.7, 100000, 0.5, 1.3),
+                                                  (1.5, 1, 0.9, 1.0), (0.0, 40, 0.9, 1.2), (2.0, 100000, 1.0, 1.0)])
+def test_sample_matches_plain(V, temp, top_k, top_p, pen):
+    rows = 12
+    lg = rnd((rows, V), 41, scale=2.0)
+    lg[3, 10] = lg[3, 200] = lg[3].max() + 0.5                                  # equal maxima
+    recent = [[(7 * r + i * i) % V for i in range(r % 5 + (r > 6) * 60)] for r in range(rows)]
+    rec = torch.full((rows, 64), -1, dtype=torch.int32)
+    for r, ids in enumerate(recent):
+        ids = ids[-64:]
+        rec[r, :len(ids)] = torch.tensor(ids, dtype=torch.int32)
+    streams = torch.arange(rows, dtype=torch.int32) * 3
+    for counter in (0, 1, 17):
+        counters = torch.full((rows,), counter, dtype=torch.int32)
+        got = ops().sample(lg.to(DEV), temp, top_k, top_p, pen, rec.to(DEV), 1234, streams.to(DEV),
+                           counters.to(DEV)).cpu().tolist()
+        want = [P.sample(lg[r], temp, top_k, top_p, pen, recent[r][-64:], P.philox_uniform(1234, int(streams[r]), counter))
+                for r in range(rows)]
+        assert got == want
+
+
+def test_sample_follows_the_distribution():
+    """Many draws from one row: frequencies follow exp(l / temp) over the kept candidates."""
+    V, n = 50, 4000
+    lg = rnd((1, V), 42, scale=1.5).repeat(n, 1).contiguous()
+    got = ops().sample(lg.to(DEV), 1.0, 8, 1.0, 1.0, None, 99, torch.zeros(n, dtype=torch.int32, device=DEV),
+                       torch.arange(n, dtype=torch.int32, device=DEV)).cpu()
+    top = torch.topk(lg[0], 8).indices
+    assert set(got.tolist()) <= set(top.tolist())
+    p = torch.softmax(lg[0][top].double(), 0)
+    freq = torch.tensor([(got == i).sum().item() for i in top], dtype=torch.double) / n
+    assert (freq - p).abs().max().item() < 4 * math.sqrt(0.25 / n)
