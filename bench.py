@@ -1,0 +1,256 @@
+"""Decode and prefill throughput of the Llama-3.1-8B shape on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at the given batch with every
+sequence's cache filled to the context length; a step is one decode step (forward pass of one
+token per sequence plus the greedy pick), replayed from a CUDA graph and timed with CUDA events.
+``e2e`` is the same through ``Engine.generate`` (host token ids in, host token ids out, one
+upload of the step's description and one read-back of the sampled ids per step).
+``prefill`` is one step of 2,048 prompt tokens.  ``roofline`` divides the bytes a decode step
+has to read (every weight once, and the cache of the live sequences) by its time.
+Weights are random (seeded), token ids are seeded-uniform: no dataset, no checkpoint.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA_3_1_8B = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 4096, "num_hidden_layers": 32, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336, "vocab_size": 128256,
+    "rope_theta": 500000.0, "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                             "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "max_position_embeddings": 131072, "tie_word_embeddings": False, "torch_dtype": "bfloat16",
+}
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(d.get(k), (int, float)):
+                    out[k] = float(d[k])
+            out["source"] = "measured"
+            return out
+        except (OSError, ValueError):
+            pass
+    out = dict(FALLBACK_PEAKS)
+    out["source"] = "fallback"
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def fill_cache(eng, slots, length, vocab, seed):
+    """Brings every slot to ``length`` positions by real prefill steps of random tokens."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    chunk = 2048
+    group = max(1, 16384 // chunk)
+    for g0 in range(0, len(slots), group):
+        part = slots[g0:g0 + group]
+        done = 0
+        while done < length:
+            n = min(chunk, length - done)
+            eng.step(part, [rng.integers(0, vocab, size=n).tolist() for _ in part], None)
+            done += n
+
+
+def decode_run(eng, batch, steps, warmup, vocab, context, clocks=None):
+    """Times ``steps`` graph-replayed decode steps at ``batch`` sequences whose caches hold
+    about ``context`` positions (the last timed step reaches exactly ``context``)."""
+    import numpy as np
+    import torch
+    slots = [eng.alloc_slot() for _ in range(batch)]
+    fill_cache(eng, slots, context - steps - warmup - 1, vocab, seed=batch)
+    dec = eng._decoder
+    rng = np.random.default_rng(1000 + batch)
+    toks = [[int(x)] for x in rng.integers(0, vocab, size=batch)]
+    dec.step(slots, toks)                                   # captures the graph for this shape
+    for _ in range(warmup):
+        _, ids = dec.step(slots, toks)
+    torch.cuda.synchronize()
+    if clocks is not None:
+        clocks.start()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        _, ids = dec.step(slots, toks)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end)
+    info = clocks.stop() if clocks is not None else None
+    eng.stepper.check_status()
+    launches = dec.launches_last_step
+    kv_len = eng.cache.length(slots[0])
+    for s in slots:
+        eng.free_slot(s)
+    return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "launches_per_step": launches,
+            "kv_len": kv_len, "clocks": info}
+
+
+def e2e_run(eng, batch, steps, vocab, context):
+    """The same decode steps through the public entry point: host ids in, host ids out."""
+    import numpy as np
+    rng = np.random.default_rng(77)
+    prompts = [rng.integers(0, vocab, size=context - steps - 1).tolist() for _ in range(batch)]
+    eng.generate(prompts, max_tokens=3, temp=0.0, rep_pen=1.0, stop_token_ids=[])          # warm: captures this shape
+    out = eng.generate(prompts, max_tokens=steps + 1, temp=0.0, rep_pen=1.0, stop_token_ids=[])
+    st = eng.last_stats
+    assert all(len(o) == steps + 1 for o in out)
+    # the first token of each sequence comes from the prefill step; the decode clock covers the rest
+    return {"tok_s": batch * steps / st.decode_seconds, "h2d": eng.stepper.builder.last_upload_bytes, "d2h": batch * 4 + 4}
+
+
+def prefill_run(eng, tokens, vocab, reps=3):
+    import numpy as np
+    import torch
+    rng = np.random.default_rng(5)
+    best = None
+    for r in range(reps + 1):
+        s = eng.alloc_slot()
+        ids = rng.integers(0, vocab, size=tokens).tolist()
+        ctx = eng.stepper.prepare([s], [ids], "last")
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        eng.model.forward(ctx, eng.cache)
+        b.record()
+        torch.cuda.synchronize()
+        eng.stepper.finish(ctx)
+        eng.free_slot(s)
+        if r > 0:
+            ms = a.elapsed_time(b)
+            best = ms if best is None else min(best, ms)
+    return best
+
+
+def model_flops_per_token(cfg, n_layers):
+    d, ff, nh, nkv, hd, V = (cfg["hidden_size"], cfg["intermediate_size"], cfg["num_attention_heads"],
+                             cfg["num_key_value_heads"], cfg["head_dim"], cfg["vocab_size"])
+    per_layer = 2 * (d * (nh + 2 * nkv) * hd + nh * hd * d + 3 * d * ff)
+    return per_layer * n_layers, 2 * d * V
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (reported)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "SwankyMan88/ithaca is a Windows-only C++ program (windows.h, nvcuda.dll, build.bat) with no "
+                          "Python package or POSIX build: pip cannot install it here and it cannot run on Linux"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU only (this library has no multi-GPU path); --gpus {args.gpus} is not run")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    from ithaca_b200 import Engine
+
+    pk = peaks()
+    cfg = dict(LLAMA_3_1_8B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    n_layers = cfg["num_hidden_layers"]
+    vocab = cfg["vocab_size"]
+    max_b = args.batch if args.no_points else max(args.batch, 64)
+    eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max_b * (CONTEXT + 64), ctx=CONTEXT + 64)
+
+    clocks = ClockSampler()
+    main_run = decode_run(eng, args.batch, args.steps, args.warmup, vocab, CONTEXT, clocks)
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = round(decode_run(eng, b, min(args.steps, 32), args.warmup, vocab, CONTEXT)["tok_s"], 1)
+    e2e = e2e_run(eng, args.batch, min(args.steps, 32), vocab, CONTEXT)
+    pre_ms = prefill_run(eng, PREFILL_TOKENS, vocab)
+
+    layer_flops, head_flops = model_flops_per_token(cfg, n_layers)
+    attn_flops = 4 * cfg["num_attention_heads"] * cfg["head_dim"] * PREFILL_TOKENS * PREFILL_TOKENS / 2 * n_layers
+    pre_flops = layer_flops * PREFILL_TOKENS + attn_flops + head_flops
+    weight_bytes = eng.model.weight_bytes()
+    kv_bytes = eng.cache.bytes_per_token() * main_run["kv_len"] * args.batch
+    achieved = (weight_bytes + kv_bytes) / (main_run["ms_per_step"] / 1e3) / 1e9
+    line = {
+        "metric": "decode tok/s @ batch 8, context 4096 (Llama-3.1-8B shape)" if args.batch == 8 else
+                  f"decode tok/s @ batch {args.batch}, context 4096 (Llama-3.1-8B shape)",
+        "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",
+        "config": {"model": "Llama-3.1-8B shape", "layers": n_layers, "layers_of_model": full_layers,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": vocab, "global_batch": args.batch,
+                   "seq_len": CONTEXT, "parallelism": "single GPU", "l2": "inputs larger than L2 (weights + cache)",
+                   "cache_page": 64, "peaks": pk["source"]},
+        "clocks": main_run["clocks"],
+        "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tok/s", "h2d_bytes_per_step": e2e["h2d"],
+                "d2h_bytes_per_step": e2e["d2h"]},
+        "gpu_launches": main_run["launches_per_step"] * args.steps,
+        "prefill": {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
+                    "frac": round(pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

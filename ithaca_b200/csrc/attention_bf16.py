@@ -84,7 +84,7 @@ def decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, kv_len
         out = torch.empty_like(q)
     _check(m.ik_attn_decode(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(part_o), _ptr(part_ml),
                             _ptr(kv_lens), _ptr(table), table.stride(0), n_seqs, n_heads, nkv, scale, window,
-                            page_size, n_pages, chunk_pages, n_splits, _ptr(status), _stream()), "attention decode")
+                            page_size, n_pages, chunk_pages, n_splits, _ptr(status), _stream()), "attention decode", kernels=2)
     return out
 
 

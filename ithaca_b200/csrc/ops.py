@@ -46,7 +46,17 @@ def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> No
         raise KernelError(f"{name} must be {dtype}, found {t.dtype}")
 
 
-def _check(status: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernel-library calls made so far in this process (each is one or two kernel launches)."""
+    return _launches
+
+
+def _check(status: int, what: str, kernels: int = 1) -> None:
+    global _launches
+    _launches += kernels
     if status == 0:
         return
     if status == -1:

@@ -21,6 +21,7 @@ from ..sampling.sampler import Sampler, SamplingOptions
 from ..weights.random_init import random_tensors
 from .generate import GenerationOptions, GenStats, generate_loop
 from .model import build_model, load_model, weight_manifest
+from .graph import GraphDecoder
 from .step import Stepper
 
 
@@ -30,13 +31,14 @@ def _round_up(n: int, m: int) -> int:
 
 class Engine:
     def __init__(self, model_dir: Optional[str] = None, *, dtype: str = "bfloat16", device: str = "cuda:0",
-                 max_tokens: Optional[int] = None, max_slots: Optional[int] = None, ctx: Optional[int] = None,
+                 max_tokens: Optional[int] = None, max_slots: Optional[int] = None, ctx: Optional[int] = None, graphs: bool = True,
                  _model=None, _config=None):
         """``max_tokens``: the most positions live sequences hold at any time, each rounded up
         to a multiple of 64; it sizes the cache (default: 8 sequences of ``ctx``).
         ``ctx``: the most positions one sequence may hold (default: the model's
         ``max_position_embeddings``, as the reference caps ``--ctx`` at the trained
-        context, src/model.cpp:259)."""
+        context, src/model.cpp:259).  ``graphs``: replay decode steps of the generation
+        loop from CUDA graphs."""
         if not torch.cuda.is_available():
             raise RuntimeError("ithaca_b200 runs on a CUDA device only; none is available")
         torch.cuda.set_device(device)
@@ -55,7 +57,7 @@ class Engine:
         self.stepper = Stepper(self.model, self.cache, max_position=self.context_length)
         self.last_stats: Optional[GenStats] = None
         self._sampler: Optional[Sampler] = None
-        self._decoder = None
+        self._decoder = GraphDecoder(self.stepper) if graphs else None
 
     @classmethod
     def from_random(cls, config: Dict[str, Any], seed: int = 0, *, dtype: str = "bfloat16",

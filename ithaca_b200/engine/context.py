@@ -41,7 +41,9 @@ class ContextBuilder:
 
     def __init__(self, device: str):
         self.device = device
+        self.last_upload_bytes = 0
         self._pinned: Optional[torch.Tensor] = None
+        self._copied: Optional[torch.cuda.Event] = None      # the last upload from the staging buffer
 
     def _staging(self, n: int) -> torch.Tensor:
         if self._pinned is None or self._pinned.numel() < n:
@@ -75,6 +77,8 @@ class ContextBuilder:
             offs.append(total)
             total += (s + 3) // 4 * 4
         total = max(total, 4)
+        if self._copied is not None:
+            self._copied.synchronize()                        # the staging buffer is free again
         stage = self._staging(total)
         sn = stage.numpy()
         for p, o in zip(parts, offs):
@@ -86,6 +90,10 @@ class ContextBuilder:
                 raise ValueError("the context buffer is too small for this step")
             dev = into
         dev[:total].copy_(stage[:total], non_blocking=True)
+        if self._copied is None:
+            self._copied = torch.cuda.Event()
+        self._copied.record()
+        self.last_upload_bytes = total * 4
 
         def view(i):
             return dev[offs[i]:offs[i] + sizes[i]]
