@@ -238,3 +238,59 @@ IK_EXPORT int ik_sample(const float* logits, int ldl, float* work, int* out, int
                                            n_recent, (uint64_t)seed, streams, counters);
     IK_LAUNCH_STATUS();
 }
+
+// ------------------------------------------------------------------------------------------
+// The variant that allocates nothing (see sampling_static.h for who needs it and its rules).
+#include <stdio.h>
+#include <mutex>
+#include "sampling_static.h"
+
+namespace {
+
+// The scratch of ik_sample_static.  In host code this name is only a handle for
+// cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float g_static_work[IK_SAMPLE_STATIC_MAX_FLOATS];
+
+constexpr int STATIC_MAX_DEVICES = 64;
+float* g_static_work_addr[STATIC_MAX_DEVICES];      // per device: the array's address there, null until looked up
+std::mutex g_static_mutex;
+
+// The device address of g_static_work on the current device (looked up once per device).
+int static_work_address(float** addr) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= STATIC_MAX_DEVICES) return IK_BAD_ARGUMENT;
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_work_addr[dev]) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_static_work);
+        if (e != cudaSuccess) return (int)e;
+        if (!p) return IK_BAD_ARGUMENT;
+        g_static_work_addr[dev] = p;
+    }
+    *addr = g_static_work_addr[dev];
+    return IK_OK;
+}
+
+}  // namespace
+
+IK_EXPORT int ik_sample_static(const float* logits, int ldl, int* out, int rows, int V, float temperature, int top_k,
+                               float top_p, float rep_pen, const int* recent, int n_recent, unsigned long long seed,
+                               const int* streams, const int* counters, cudaStream_t stream) {
+    if (rows < 0 || V <= 0 || ldl < V || n_recent < 0 || !(rep_pen > 0.f) || !(top_p > 0.f)) return IK_BAD_ARGUMENT;
+    if ((long long)rows * V > (long long)IK_SAMPLE_STATIC_MAX_FLOATS) {
+        fprintf(stderr, "ik_sample_static: %d rows x %d logits = %lld floats of scratch, the static array holds %d; "
+                        "use ik_sample with scratch of your own\n", rows, V, (long long)rows * V,
+                IK_SAMPLE_STATIC_MAX_FLOATS);
+        return IK_SAMPLE_STATIC_TOO_LARGE;
+    }
+    if (rows == 0) return IK_OK;
+    float* work = nullptr;
+    const int st = static_work_address(&work);
+    if (st != IK_OK) return st;
+    // sample_kernel copies each row's logits into `work` before it reads it: stale contents never show
+    sample_kernel<<<rows, ST, 0, stream>>>(logits, ldl, work, out, V, temperature, top_k, top_p, rep_pen, recent,
+                                           n_recent, (uint64_t)seed, streams, counters);
+    IK_LAUNCH_STATUS();
+}
