@@ -57,7 +57,7 @@ class Engine:
         self.stepper = Stepper(self.model, self.cache, max_position=self.context_length)
         self.last_stats: Optional[GenStats] = None
         self._sampler: Optional[Sampler] = None
-        self._decoder = GraphDecoder(self.stepper) if graphs else None
+        self._decoder = GraphDecoder(self.stepper) if graphs and getattr(self.model, "graph_safe", False) else None
 
     @classmethod
     def from_random(cls, config: Dict[str, Any], seed: int = 0, *, dtype: str = "bfloat16",

@@ -1,0 +1,107 @@
+"""The command line, in the manner of the reference's prompt mode (src/main.cpp:945-1144).
+
+Options the reference has keep its names and meanings: ``--model/-m``, ``--prompt/-p``,
+``-n`` (default 128), ``--temp`` (default 0), ``--ctx/-c``, ``--bench`` (prompt of 512 and
+128 generated tokens, three runs after a warm-up of 64, printed as one ``BENCH`` line,
+src/main.cpp:1047-1068).  There is no tokenizer in this library, so a prompt is a list of
+token ids (``-p "1,2,3"``); ``-p`` may be given several times for a batch.  After the run
+it prints ``[prompt N tok @ X tok/s | gen M tok @ Y tok/s]`` (src/main.cpp:1140).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+from typing import List, Optional
+
+
+def _ids(text: str) -> List[int]:
+    try:
+        return [int(x) for x in text.replace(",", " ").split()]
+    except ValueError:
+        raise SystemExit(f"a prompt is a list of token ids separated by commas or spaces, found {text!r}")
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="ithaca_b200", description="generate tokens with a model folder on one B200")
+    ap.add_argument("--model", "-m", help="folder with config.json and *.safetensors")
+    ap.add_argument("--random", metavar="CONFIG.json", help="instead of --model: random weights for this configuration")
+    ap.add_argument("--seed", type=int, default=0, help="seed of the random weights (--random) and of sampling")
+    ap.add_argument("--prompt", "-p", action="append", default=[], help="token ids, e.g. \"1,2,3\"; repeatable")
+    ap.add_argument("--prompt-file", help="a file with one prompt (token ids) per line")
+    ap.add_argument("-n", type=int, default=128, dest="n", help="tokens to generate per prompt (default 128)")
+    ap.add_argument("--temp", type=float, default=0.0, help="temperature; 0 = greedy (default)")
+    ap.add_argument("--top-k", type=int, default=40)
+    ap.add_argument("--top-p", type=float, default=0.9)
+    ap.add_argument("--rep-pen", type=float, default=1.1, help="repetition penalty over the last 64 generated ids")
+    ap.add_argument("--stop-ids", default=None, help="stop token ids (default: the model's eos_token_id)")
+    ap.add_argument("--ctx", "-c", type=int, default=None, help="most positions per sequence (default: the model's)")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--max-tokens", type=int, default=None, help="cache size in positions (default: 8 sequences of ctx)")
+    ap.add_argument("--bench", action="store_true", help="pp512 / tg128, three runs, one BENCH line")
+    ap.add_argument("--describe", action="store_true", help="print the model's layers and schedule, then exit")
+    return ap
+
+
+def _engine(args):
+    from .api import Engine
+    if args.random:
+        with open(args.random) as f:
+            cfg = json.load(f)
+        return Engine.from_random(cfg, args.seed, dtype=args.dtype, max_tokens=args.max_tokens, ctx=args.ctx)
+    if not args.model:
+        raise SystemExit("give --model DIR (or --random CONFIG.json)")
+    return Engine(args.model, dtype=args.dtype, max_tokens=args.max_tokens, ctx=args.ctx)
+
+
+def _bench(eng, name: str, load_s: float) -> None:
+    import numpy as np
+    import torch
+    vocab = eng.model.spec.vocab_size
+    rng = np.random.default_rng(0)
+    eng.generate([rng.integers(0, vocab, 64).tolist()], max_tokens=2, temp=0.0, rep_pen=1.0, stop_token_ids=[])
+    pp, tg = [], []
+    for _ in range(3):
+        eng.generate([rng.integers(0, vocab, 512).tolist()], max_tokens=129, temp=0.0, rep_pen=1.0, stop_token_ids=[])
+        st = eng.last_stats
+        pp.append(512 / st.prefill_seconds)
+        tg.append(128 / st.decode_seconds)
+    vram = torch.cuda.max_memory_allocated() / 2**20
+    print(f"BENCH model={name} load_s={load_s:.2f} pp512={sum(pp) / 3:.1f} tg128={sum(tg) / 3:.2f} vram_mb={vram:.0f}")
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    args = build_parser().parse_args(argv)
+    t0 = time.perf_counter()
+    eng = _engine(args)
+    load_s = time.perf_counter() - t0
+    spec = eng.model.spec
+    print(f"[{args.model or args.random} | {spec.architecture} | {len(spec.schedule)} layers | {args.dtype} | "
+          f"opened in {load_s * 1e3:.0f} ms]", file=sys.stderr)
+    if args.describe:
+        from ..config import describe
+        print("\n".join(describe(spec)))
+        return 0
+    if args.bench:
+        _bench(eng, args.model or args.random, load_s)
+        return 0
+    prompts = [_ids(p) for p in args.prompt]
+    if args.prompt_file:
+        with open(args.prompt_file) as f:
+            prompts += [_ids(line) for line in f if line.strip()]
+    if not prompts:
+        raise SystemExit("give at least one --prompt (token ids)")
+    stops = _ids(args.stop_ids) if args.stop_ids is not None else None
+    out = eng.generate(prompts, max_tokens=args.n, temp=args.temp, top_k=args.top_k, top_p=args.top_p,
+                       rep_pen=args.rep_pen, seed=args.seed, stop_token_ids=stops)
+    for o in out:
+        print(",".join(str(t) for t in o))
+    st = eng.last_stats
+    print(f"[prompt {st.prompt_tokens} tok @ {st.prefill_tps:.1f} tok/s | gen {st.gen_tokens} tok @ {st.gen_tps:.1f} tok/s]",
+          file=sys.stderr)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -45,6 +45,14 @@ class DecoderModel:
             tensors[spec.head.weights["weight"]] = self.embedding.table      # one copy on the device for both
         self.head = OutputHead(spec.head, tensors, runtime)
 
+    @property
+    def graph_safe(self) -> bool:
+        """True when every mixer and feed-forward says that a captured step may be replayed for
+        other slots and positions (they read those from the step's device arrays, never from
+        host values).  A part that does not say so is stepped eagerly."""
+        return all(getattr(l.mixer, "graph_safe", False) and getattr(l.feed_forward, "graph_safe", False)
+                   for l in self.layers)
+
     def cache_requests(self) -> Dict[int, List[object]]:
         out: Dict[int, List[object]] = {}
         for e in self.spec.schedule:

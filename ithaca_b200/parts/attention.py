@@ -27,6 +27,8 @@ from .linear import Linear
 
 
 class Attention:
+    graph_safe = True       # reads slots, positions and lengths from device arrays only
+
     @classmethod
     def manifest(cls, spec: PartSpec) -> Dict[str, TensorReq]:
         d, nh, nkv, hd = spec["hidden_size"], spec["n_heads"], spec["n_kv_heads"], spec["head_dim"]

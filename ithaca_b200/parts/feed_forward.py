@@ -16,6 +16,8 @@ from .linear import Linear
 
 
 class GatedMLP:
+    graph_safe = True
+
     @classmethod
     def manifest(cls, spec: PartSpec) -> Dict[str, TensorReq]:
         d, ff = spec["hidden_size"], spec["intermediate_size"]
