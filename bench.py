@@ -186,6 +186,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="run one part only and print its figures (for profiling a small case)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -208,8 +210,17 @@ def main():
         cfg["num_hidden_layers"] = args.layers
     n_layers = cfg["num_hidden_layers"]
     vocab = cfg["vocab_size"]
-    max_b = args.batch if args.no_points else max(args.batch, 64)
+    max_b = args.batch if (args.no_points or args.only != "all") else max(args.batch, 64)
     eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max_b * (CONTEXT + 64), ctx=CONTEXT + 64)
+
+    if args.only == "decode":
+        r = decode_run(eng, args.batch, args.steps, args.warmup, vocab, CONTEXT)
+        print(json.dumps({"only": "decode", "batch": args.batch, "layers": n_layers, **{k: v for k, v in r.items() if k != "clocks"}}))
+        return 0
+    if args.only == "prefill":
+        ms = prefill_run(eng, PREFILL_TOKENS, vocab, reps=max(1, args.steps))
+        print(json.dumps({"only": "prefill", "layers": n_layers, "tokens": PREFILL_TOKENS, "ms": ms}))
+        return 0
 
     clocks = ClockSampler()
     main_run = decode_run(eng, args.batch, args.steps, args.warmup, vocab, CONTEXT, clocks)

@@ -30,7 +30,7 @@ _COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcom
                  "--expt-relaxed-constexpr"]
 
 # The always-needed kernels.  Specialised modules are listed in SPECIALISED.
-CORE_SOURCES = ["elementwise.cu", "gemm_simt.cu", "gemm_mma.cu", "attention_simt.cu", "sampling.cu"]
+CORE_SOURCES = ["elementwise.cu", "gemm_simt.cu", "gemm_mma.cu", "gemm_tcgen05.cu", "attention_simt.cu", "sampling.cu"]
 
 _lock = threading.Lock()
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -1,0 +1,344 @@
+// bfloat16 product on the fifth-generation tensor cores of sm_100a:
+//   Y[M, N] (+)= X[M, K] * W[N, K]^T,  X and W bfloat16 with K contiguous, float accumulation in TMEM.
+//
+// The weight matrix is the 128-row operand (one TMEM lane per output feature) and the tokens
+// are the N-operand (one TMEM column per token, BN = 32 .. 256 of them per block), for prefill
+// and decode alike: the epilogue then writes, for each token, 32 consecutive features per warp
+// instruction (coalesced), and a handful of decode tokens wastes no tensor work.
+//
+// One block computes one 128 x BN tile (optionally one slice of K):
+//   warp 0      one lane issues the TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the
+//               128 x 64 weight tile and the BN x 64 token tile of each K step into a ring of
+//               shared-memory stages; completion is counted on the stage's "full" mbarrier.
+//   warp 1      allocates TMEM; one lane issues four tcgen05.mma (K = 16 each) per stage and
+//               commits them to the stage's "empty" mbarrier; after the last stage it commits to
+//               the "accumulator ready" mbarrier.  Frees TMEM at the end.
+//   warps 2..5  read the accumulator with tcgen05.ld (each warp its 32 lanes) and store it.
+// Tails in M, N and K are zero-filled by TMA and masked in the epilogue.  No multicast, no
+// clusters.
+//
+// Every wait on an mbarrier is bounded: after about a second without progress the waiting
+// thread sets the status word to IK_STATUS_GEMM_TIMEOUT, raises the block's abort flag and
+// every role leaves its loop; TMEM is freed and the block returns.  Blocks that start after
+// the status word is set return at once.  Needs K % 8 == 0 and 16-byte aligned rows (TMA
+// strides); the host entry returns IK_UNSUPPORTED otherwise.
+#include <cuda.h>
+#include "common.cuh"
+
+#define IK_STATUS_GEMM_TIMEOUT 4
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+constexpr int BM = 128;              // weight rows per tile = TMEM lanes
+constexpr int BK = 64;               // 64 bf16 = 128 bytes = one swizzle row
+constexpr int THREADS = 192;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Waits for the phase with the given parity to complete.  Gives up after ~1 s (or as soon as
+// another thread of the block has given up) and returns false.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    if (mbar_test(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer();
+    for (int spin = 0;; spin++) {
+        if (mbar_test(bar, parity)) return true;
+        if ((spin & 63) == 63) {
+            if (*abort_flag) return false;
+            if (globaltimer() - t0 > 1000000000ull) {
+                *abort_flag = 1;
+                if (status) atomicExch(status, IK_STATUS_GEMM_TIMEOUT);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        :: "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle, groups of
+// 8 rows 1024 bytes apart (version 1 = sm_100).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address
+    d |= (uint64_t)1 << 16;                               // leading byte offset (unused under swizzle) = 1
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                               // descriptor version
+    d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: D float, A and B bfloat16, both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 :: "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    #pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN> struct Cfg {
+    static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (200 * 1024 / STAGE) > 8 ? 8 : (200 * 1024 / STAGE);
+    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr int SMEM = STAGES * STAGE + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+// map_w: [N rows, K] box {64, 128};  map_x: [M rows, K] box {64, BN}.
+// out: Y (float or bf16) when partial == nullptr, else partial sums [splits][M][N] float.
+template <int BN, typename TY>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    TY* __restrict__ Y, float* __restrict__ partial, int M, int N, int K, int ldy, int accumulate,
+                    int kb_per_split, int* status) {
+    typedef Cfg<BN> C;
+    extern __shared__ unsigned char smem_raw[];
+    if (status && *(volatile int*)status == IK_STATUS_GEMM_TIMEOUT) return;     // an earlier block gave up
+    unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(tiles + C::STAGES * C::STAGE);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* acc_ready = empty + C::STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BM;                    // first weight row (output feature)
+    const int m0 = blockIdx.y * BN;                    // first token
+    const int nkb_total = (K + BK - 1) / BK;
+    const int kb0 = blockIdx.z * kb_per_split;
+    const int nkb = min(kb_per_split, nkb_total - kb0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+        mbar_init(acc_ready, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" :: "l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" :: "l"(&map_x) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(smem_u32(tmem_slot)), "r"((uint32_t)C::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int armed = 0;
+            for (int i = 0; i < nkb; i++) {
+                const int s = i % C::STAGES;
+                if (!mbar_wait(empty + s, ((i / C::STAGES) & 1) ^ 1, abort_flag, status)) break;
+                unsigned char* a = tiles + s * C::STAGE;
+                mbar_expect_tx(full + s, C::STAGE);
+                tma_load_2d(a, &map_w, (kb0 + i) * BK, n0, full + s);
+                tma_load_2d(a + C::A_BYTES, &map_x, (kb0 + i) * BK, m0, full + s);
+                armed = i + 1;
+            }
+            if (*abort_flag) {
+                // leave no copy of this block in flight: wait (bounded) for the stages that were armed last
+                for (int i = max(0, armed - C::STAGES); i < armed; i++) {
+                    const unsigned long long t0 = globaltimer();
+                    while (!mbar_test(full + i % C::STAGES, (i / C::STAGES) & 1) && globaltimer() - t0 < 2000000ull) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(BN);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; i++) {
+                const int s = i % C::STAGES;
+                ok = mbar_wait(full + s, (i / C::STAGES) & 1, abort_flag, status);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a = smem_u32(tiles + s * C::STAGE), b = a + C::A_BYTES;
+                #pragma unroll
+                for (int j = 0; j < BK / 16; j++)
+                    umma(tmem_base, umma_desc(a + j * 32), umma_desc(b + j * 32), idesc, (i | j) != 0);
+                umma_commit(empty + s);                 // the stage is free once these MMAs have read it
+            }
+            if (ok) umma_commit(acc_ready);
+        }
+    } else {
+        // epilogue: warp w owns TMEM lanes 32 * (w % 4) .. + 31
+        const int quarter = warp & 3;
+        const int feature = n0 + quarter * 32 + lane;
+        if (nkb > 0 && mbar_wait(acc_ready, 0, abort_flag, status)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            #pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (m0 + c0 >= M) break;
+                float v[16];
+                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c0, v);
+                if (feature < N) {
+                    #pragma unroll
+                    for (int c = 0; c < 16; c++) {
+                        const int m = m0 + c0 + c;
+                        if (m >= M) break;
+                        if (partial) {
+                            partial[((size_t)blockIdx.z * M + m) * N + feature] = v[c];
+                        } else {
+                            const size_t o = (size_t)m * ldy + feature;
+                            float r = v[c];
+                            if (accumulate) r += ik_ld(Y, o);
+                            ik_st(Y, o, r);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
+    }
+}
+
+// Adds the K slices in slice order and writes Y.
+template <typename TY>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, TY* __restrict__ Y, int M, int N, int ldy,
+                                     int splits, int accumulate) {
+    const size_t total = (size_t)M * N;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        float s = 0.f;
+        for (int z = 0; z < splits; z++) s += partial[(size_t)z * total + idx];
+        const size_t m = idx / N, n = idx - m * N;
+        const size_t o = m * ldy + n;
+        if (accumulate) s += ik_ld(Y, o);
+        ik_st(Y, o, s);
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// rows x K bfloat16 matrix, K contiguous, row stride ld elements; box = 64 x box_rows, 128-byte swizzle, zero fill.
+int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
+    EncodeTiled enc = encode_fn();
+    if (!enc) return IK_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? IK_OK : IK_BAD_ARGUMENT;
+}
+
+template <int BN, typename TY>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial, int M, int N, int K, int ldy,
+           int accumulate, int splits, int* status, cudaStream_t stream) {
+    typedef Cfg<BN> C;
+    auto kern = gemm_tcgen05_kernel<BN, TY>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    const int nkb = (K + BK - 1) / BK;
+    const int per = (nkb + splits - 1) / splits;
+    dim3 grid((N + BM - 1) / BM, (M + BN - 1) / BN, (nkb + per - 1) / per);
+    kern<<<grid, THREADS, C::SMEM, stream>>>(mw, mx, (TY*)Y, grid.z > 1 ? partial : nullptr, M, N, K, ldy, accumulate,
+                                             per, status);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    if (grid.z > 1) {
+        const size_t total = (size_t)M * N;
+        const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+        splitk_reduce_kernel<TY><<<blocks, 256, 0, stream>>>(partial, (TY*)Y, M, N, ldy, (int)grid.z, accumulate);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    return IK_OK;
+}
+
+}  // namespace
+
+// Token-tile width the kernel will use for M tokens.
+IK_EXPORT int ik_gemm_tcgen05_tile(int M) { return M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
+
+// splits > 1 needs `partial`: splits * M * N floats of scratch owned by the caller.
+// status: device int; set to 4 if a block gave up waiting (the result is then not to be used).
+IK_EXPORT int ik_gemm_tcgen05(const void* X, const void* W, void* Y, int y_dtype, float* partial, int M, int N, int K,
+                              int ldx, int ldw, int ldy, int accumulate, int splits, int* status, cudaStream_t stream) {
+    if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || ldy < N || splits < 1) return IK_BAD_ARGUMENT;
+    if (y_dtype != IK_F32 && y_dtype != IK_BF16) return IK_BAD_ARGUMENT;
+    if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return IK_UNSUPPORTED;
+    if (splits > 1 && !partial) return IK_BAD_ARGUMENT;
+    if (M == 0) return IK_OK;
+    const int bn = ik_gemm_tcgen05_tile(M);
+    CUtensorMap mw, mx;
+    int st = make_map(&mw, W, N, K, ldw, BM);
+    if (st != IK_OK) return st;
+    st = make_map(&mx, X, M, K, ldx, bn);
+    if (st != IK_OK) return st;
+#define IK_TC(BN_)                                                                                                       \
+    return y_dtype == IK_F32 ? launch<BN_, float>(mw, mx, Y, partial, M, N, K, ldy, accumulate, splits, status, stream)    \
+                             : launch<BN_, bf16>(mw, mx, Y, partial, M, N, K, ldy, accumulate, splits, status, stream)
+    switch (bn) {
+        case 32: IK_TC(32);
+        case 64: IK_TC(64);
+        case 128: IK_TC(128);
+        default: IK_TC(256);
+    }
+#undef IK_TC
+}

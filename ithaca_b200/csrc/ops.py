@@ -73,12 +73,26 @@ _SIGNATURES = {
     "ik_rope_append": [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "ik_gemm_bf16_mma": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "ik_gemm_tcgen05": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "ik_gemm_tcgen05_tile": [_i],
     "ik_attention_simt": [_vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp],
     "ik_argmax": [_vp, _i, _vp, _i, _i, _vp],
     "ik_sample": [_vp, _i, _vp, _vp, _i, _i, _f, _i, _f, _f, _vp, _i, _u64, _vp, _vp, _vp],
 }
 
 _lib = None
+_status = {}
+
+
+def device_status(device) -> torch.Tensor:
+    """The int32 status word kernels set when they meet something they refuse to do (an index
+    out of range, a wait that ran out); one per device, shared by every runtime on it."""
+    key = str(torch.device(device))
+    t = _status.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[key] = t
+    return t
 
 
 def lib():
@@ -201,6 +215,49 @@ def gemm_bf16_mma(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] 
     if st == -2:
         return None
     _check(st, "gemm_bf16_mma")
+    return out
+
+
+N_SM = 148
+
+
+def tcgen05_splits(M: int, N: int, K: int) -> int:
+    """K slices for the tcgen05 product: as many as fill the SMs when the output has few tiles.
+    Each slice keeps at least four 64-wide K steps."""
+    tiles = -(-N // 128) * -(-M // lib().ik_gemm_tcgen05_tile(M))
+    if tiles >= N_SM:
+        return 1
+    return max(1, min(N_SM // tiles, -(-K // 64) // 4))
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=torch.float32,
+                 accumulate: bool = False, splits: Optional[int] = None,
+                 status: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """bfloat16 operands on the tcgen05 tensor cores (TMA-fed, accumulators in TMEM).  Returns None
+    when the kernel does not take these sizes (K not a multiple of 8, unaligned rows)."""
+    _need(x, "x", torch.bfloat16, contiguous=False)
+    _need(w, "w", torch.bfloat16, contiguous=False)
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2 or x.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError(f"gemm: shapes {tuple(x.shape)} x {tuple(w.shape)}^T do not match or rows are not contiguous")
+    if K % 8 or x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16:
+        return None
+    if out is None:
+        if accumulate:
+            raise KernelError("gemm: accumulate needs an output to add to")
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _need(out, "out", contiguous=False)
+    if out.shape != (M, N) or out.stride(1) != 1:
+        raise KernelError("gemm: the output has the wrong shape")
+    if splits is None:
+        splits = tcgen05_splits(M, N, K)
+    partial = torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None
+    st = lib().ik_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(out), _code(out), _ptr(partial), M, N, K, x.stride(0),
+                               w.stride(0), out.stride(0), 1 if accumulate else 0, splits, _ptr(status), _stream())
+    if st == -2:
+        return None
+    _check(st, "gemm_tcgen05", kernels=2 if splits > 1 else 1)
     return out
 
 

@@ -107,5 +107,6 @@ class Stepper:
             if v != 0:
                 st.zero_()
                 what = {1: "a token id outside the vocabulary", 2: "a cache write without a page",
-                        3: "a cache read without a page"}.get(v, f"code {v}")
+                        3: "a cache read without a page",
+                        4: "a matrix-product block that gave up waiting for its data"}.get(v, f"code {v}")
                 raise CacheError(f"a kernel reported {what}")

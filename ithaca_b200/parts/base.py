@@ -48,7 +48,8 @@ class Runtime:
         if self.dtype not in _DTYPES:
             raise ValueError(f"dtype {self.dtype!r} is not supported (bfloat16, float32)")
         if self.status is None and self.device != "cpu" and torch.cuda.is_available():
-            self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+            from ..csrc.ops import device_status
+            self.status = device_status(self.device)
 
     @property
     def act_dtype(self) -> torch.dtype:

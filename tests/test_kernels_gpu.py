@@ -110,6 +110,37 @@ def test_gemm_bf16_tiled_large(M, N, K):
     close(got, x.double() @ w.double().T, 2e-5)
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 200, 72), (17, 4096, 512), (33, 130, 328), (64, 384, 2048),
+                                   (100, 96, 264), (200, 500, 1024), (300, 260, 72), (513, 257, 4096)])
+@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("ydt", [torch.float32, torch.bfloat16])
+def test_gemm_tcgen05(M, N, K, splits, ydt):
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    x, w = rnd((M, K), 16, torch.bfloat16), rnd((N, K), 17, torch.bfloat16)
+    ref = x.double() @ w.double().T
+    splits = min(splits, -(-K // 64))
+    got = ops().gemm_tcgen05(x.to(DEV), w.to(DEV), out_dtype=ydt, splits=splits, status=status)
+    assert got is not None and status.item() == 0
+    close(got, ref, 2e-5 if ydt == torch.float32 else 5e-3)
+    base = rnd((M, N), 18, ydt)
+    got = ops().gemm_tcgen05(x.to(DEV), w.to(DEV), out=base.to(DEV).clone(), accumulate=True, splits=splits, status=status)
+    assert status.item() == 0
+    close(got, ref + base.double(), 2e-5 if ydt == torch.float32 else 8e-3)
+
+
+def test_gemm_tcgen05_strided_rows_and_default_splits():
+    """Rows that are slices of wider matrices (row stride > K), and the split the dispatcher picks."""
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    xb, wb = rnd((40, 640), 19, torch.bfloat16).to(DEV), rnd((4096, 1024), 20, torch.bfloat16).to(DEV)
+    x, w = xb[:, 128:640], wb[:, 512:1024]
+    out = torch.zeros((40, 8192), device=DEV)
+    got = ops().gemm_tcgen05(x, w, out=out[:, 4096:], status=status)
+    assert got is not None and status.item() == 0 and ops().tcgen05_splits(40, 4096, 512) > 1
+    close(out[:, 4096:], x.double() @ w.double().T, 2e-5)
+    assert out[:, :4096].abs().max().item() == 0
+    assert ops().gemm_tcgen05(xb[:, 4:516], wb[:, :512], status=status) is None          # rows not 16-byte aligned
+
+
 def test_gemm_bf16_refuses_unaligned_k():
     x, w = rnd((4, 172), 14, torch.bfloat16), rnd((64, 172), 15, torch.bfloat16)
     assert ops().gemm_bf16_mma(x.to(DEV), w.to(DEV)) is None           # K % 8 != 0
