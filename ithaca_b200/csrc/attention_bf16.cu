@@ -1,6 +1,5 @@
 // Attention over the paged bfloat16 cache, specialised at compile time for one head size
-// (IK_HD, a multiple of 16) and one number of query heads served per decode block (IK_GC).
-// The file is compiled once per (IK_HD, IK_GC) a model needs.
+// (IK_HD, a multiple of 16).  The file is compiled once per head size a model needs.
 //
 //  * prefill: causal grouped-query flash attention.  A block owns 16*NW query tokens of one
 //    head of one sequence and walks the sequence's pages (64 keys each, aligned to absolute
@@ -8,9 +7,10 @@
 //    running maximum, the sum and the rescaling are float, in base 2 (scale * log2 e folded into
 //    the scores).  P is rounded to bfloat16 for the second product, as the reference's
 //    flash kernel rounds it to half (src/gx_kernels.cpp:535-690).
-//  * decode: one query token per sequence.  A block owns (sequence, kv head, IK_GC of the
+//  * decode: one query token per sequence.  A block owns (sequence, kv head, up to 16 of the
 //    group's query heads, one chunk of keys) and reads every key and value of its chunk
-//    exactly once for all its heads (the reference's k_attn_gqa, src/gpu_kernels.cpp:154-245).
+//    exactly once for all its heads (the reference's k_attn_gqa, src/gpu_kernels.cpp:154-245),
+//    on the same mma.sync tiles as prefill with the heads as the tile's rows.
 //    Chunks start at absolute multiples of the chunk length; each block writes an
 //    unnormalised partial (max, sum, output) and a second kernel merges the partials of a
 //    head in chunk order (k_attn_comb, src/gpu_kernels.cpp:131-150).
@@ -24,14 +24,10 @@
 #ifndef IK_HD
 #error "compile with -DIK_HD=<head size>"
 #endif
-#ifndef IK_GC
-#define IK_GC 1
-#endif
 
 namespace {
 
 constexpr int HD = IK_HD;
-constexpr int GC = IK_GC;
 constexpr int PAGE = 64;
 constexpr int LD = HD + 8;                 // padded row: consecutive rows fall into different banks
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 512, "head size must be a multiple of 16 up to 512");
@@ -226,27 +222,25 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
 }
 
 // ------------------------------------------------------------------------------------------ decode
-// Lanes per key: the largest power of two LPK <= 16 with HD % (8 LPK) == 0 and HD / LPK <= 32.
-constexpr int pick_lpk() {
-    for (int l = 16; l >= 1; l >>= 1)
-        if (HD % (8 * l) == 0 && HD / l <= 32) return l;
-    for (int l = 16; l >= 1; l >>= 1)
-        if (HD % (8 * l) == 0) return l;
-    return 1;
-}
-constexpr int LPK = pick_lpk();
-constexpr int DPL = HD / LPK;              // dims per lane (a multiple of 8)
-constexpr int GROUPS = 32 / LPK;           // keys a warp works on at once
-constexpr int KB = PAGE / (4 * GROUPS);    // keys per lane group per page: 4 warps cover a page
-static_assert(KB >= 1 && KB * 4 * GROUPS == PAGE, "a block covers one page per iteration");
-
+// One block: (sequence, kv head, up to 16 of the group's query heads, one chunk of pages).
+// The query heads are the 16 rows of the MMA tile, so every key and value of the chunk is read
+// once for all of them.  Pages stream through an NS-stage cp.async ring; each of the 4 warps
+// takes 16 of a page's 64 keys, keeps its own running (max, sum, output) and the four are
+// merged in warp order at the end.
+template <int NS>
 __global__ void __launch_bounds__(128)
 attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                    float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ kv_lens,
                    const int* __restrict__ table, int table_stride, int nh, int nkv, float scale_log2e, int window,
                    int n_pages, int chunk_pages, int n_splits, int* status) {
+    constexpr int CH = HD / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = (bf16*)smem_raw;                      // [16][LD]
+    bf16* Ks = Qs + 16 * LD;                         // [NS][PAGE][LD]
+    bf16* Vs = Ks + NS * PAGE * LD;                  // [NS][PAGE][LD]
+
     const int b = blockIdx.x, split = blockIdx.z;
-    const int G = nh / nkv, n_hc = (G + GC - 1) / GC;
+    const int G = nh / nkv, n_hc = (G + 15) / 16;
     const int kvh = blockIdx.y / n_hc, hc = blockIdx.y % n_hc;
     const int len = kv_lens[b], pos = len - 1;
     const int j0 = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
@@ -254,130 +248,152 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
     const int p_last = min((split + 1) * chunk_pages - 1, pos / PAGE);
     if (p_first > p_last) return;                                  // nothing of this chunk is visible
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = lane / LPK, li = lane % LPK;
-    const int h0 = kvh * G + hc * GC;                               // first query head of this block
-    const int n_heads_here = min(GC, G - hc * GC);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int h0 = kvh * G + hc * 16;                               // first query head of this block
+    const int n_here = min(16, G - hc * 16);
 
-    float qr[GC][DPL], o[GC][DPL], m[GC], l[GC];
-    #pragma unroll
-    for (int hh = 0; hh < GC; hh++) {
-        m[hh] = -INFINITY; l[hh] = 0.f;
-        const bf16* qp = q + ((size_t)b * nh + h0 + (hh < n_heads_here ? hh : 0)) * HD + li * DPL;
-        #pragma unroll
-        for (int d = 0; d < DPL; d++) { qr[hh][d] = __bfloat162float(qp[d]) * scale_log2e; o[hh][d] = 0.f; }
+    for (int idx = threadIdx.x; idx < 16 * CH; idx += 128) {
+        const int r = idx / CH, c = idx % CH;
+        const bool v = r < n_here;
+        cp16(Qs + r * LD + c * 8, v ? q + ((size_t)b * nh + h0 + r) * HD + c * 8 : q, v);
     }
-
-    for (int p = p_first; p <= p_last; p++) {
+    auto load_page = [&](int stage, int p) {
         int page = table[(size_t)b * table_stride + p];
         if (page < 0 || page >= n_pages) { if (threadIdx.x == 0 && status) atomicExch(status, 3); page = 0; }
-        const int key0 = (warp * GROUPS + grp) * KB;                // this lane group's first key in the page
-        const bf16* kg = k_pages + (((size_t)page * nkv + kvh) * PAGE + key0) * HD + li * DPL;
-        const bf16* vg = v_pages + (((size_t)page * nkv + kvh) * PAGE + key0) * HD + li * DPL;
-        uint4 kraw[KB][DPL / 8], vraw[KB][DPL / 8];
-        #pragma unroll
-        for (int kb = 0; kb < KB; kb++)
-            #pragma unroll
-            for (int c = 0; c < DPL / 8; c++) {
-                kraw[kb][c] = *(const uint4*)(kg + (size_t)kb * HD + c * 8);
-                vraw[kb][c] = *(const uint4*)(vg + (size_t)kb * HD + c * 8);
-            }
-        float sc[GC][KB];
-        #pragma unroll
-        for (int kb = 0; kb < KB; kb++) {
-            float kf[DPL];
-            #pragma unroll
-            for (int c = 0; c < DPL / 8; c++) {
-                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&kraw[kb][c]);
-                #pragma unroll
-                for (int e = 0; e < 4; e++) { const float2 f = __bfloat1622float2(h2[e]); kf[c * 8 + 2 * e] = f.x; kf[c * 8 + 2 * e + 1] = f.y; }
-            }
-            const int j = p * PAGE + key0 + kb;
-            const bool ok = j <= pos && j >= j0;
-            #pragma unroll
-            for (int hh = 0; hh < GC; hh++) {
-                float d = 0.f;
-                #pragma unroll
-                for (int x = 0; x < DPL; x++) d = fmaf(qr[hh][x], kf[x], d);
-                #pragma unroll
-                for (int off = LPK / 2; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
-                sc[hh][kb] = ok ? d : -INFINITY;
-            }
+        const bf16* kg = k_pages + ((size_t)page * nkv + kvh) * PAGE * HD;
+        const bf16* vg = v_pages + ((size_t)page * nkv + kvh) * PAGE * HD;
+        bf16* ks = Ks + stage * PAGE * LD;
+        bf16* vs = Vs + stage * PAGE * LD;
+        for (int idx = threadIdx.x; idx < PAGE * CH; idx += 128) {
+            const int r = idx / CH, c = idx % CH;
+            cp16(ks + r * LD + c * 8, kg + r * HD + c * 8, true);
+            cp16(vs + r * LD + c * 8, vg + r * HD + c * 8, true);
         }
-        #pragma unroll
-        for (int hh = 0; hh < GC; hh++) {
-            float mx = m[hh];
-            #pragma unroll
-            for (int kb = 0; kb < KB; kb++) mx = fmaxf(mx, sc[hh][kb]);
-            const float m_use = mx == -INFINITY ? 0.f : mx;
-            const float alpha = exp2f(m[hh] - m_use);
-            m[hh] = mx;
-            float ps = 0.f;
-            #pragma unroll
-            for (int kb = 0; kb < KB; kb++) { sc[hh][kb] = exp2f(sc[hh][kb] - m_use); ps += sc[hh][kb]; }
-            l[hh] = l[hh] * alpha + ps;
-            #pragma unroll
-            for (int x = 0; x < DPL; x++) o[hh][x] *= alpha;
-        }
-        #pragma unroll
-        for (int kb = 0; kb < KB; kb++) {
-            #pragma unroll
-            for (int c = 0; c < DPL / 8; c++) {
-                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&vraw[kb][c]);
-                #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const float2 f = __bfloat1622float2(h2[e]);
-                    #pragma unroll
-                    for (int hh = 0; hh < GC; hh++) {
-                        o[hh][c * 8 + 2 * e] = fmaf(sc[hh][kb], f.x, o[hh][c * 8 + 2 * e]);
-                        o[hh][c * 8 + 2 * e + 1] = fmaf(sc[hh][kb], f.y, o[hh][c * 8 + 2 * e + 1]);
-                    }
-                }
-            }
-        }
+    };
+    #pragma unroll
+    for (int s = 0; s < NS; s++) {
+        if (p_first + s <= p_last) load_page(s, p_first + s);
+        cp_commit();
     }
 
-    // merge the lane groups of a warp (fixed order: xor by LPK, 2 LPK, ...), then the 4 warps in order
+    uint32_t qf[HD / 16][4];
+    float o[HD / 8][4];
     #pragma unroll
-    for (int hh = 0; hh < GC; hh++) {
+    for (int d = 0; d < HD / 8; d++)
         #pragma unroll
-        for (int off = LPK; off < 32; off <<= 1) {
-            const float m_o = __shfl_xor_sync(0xffffffffu, m[hh], off);
-            const float l_o = __shfl_xor_sync(0xffffffffu, l[hh], off);
-            const float m_n = fmaxf(m[hh], m_o);
-            const float m_use = m_n == -INFINITY ? 0.f : m_n;
-            const float a = exp2f(m[hh] - m_use), bsc = exp2f(m_o - m_use);
-            l[hh] = l[hh] * a + l_o * bsc;
+        for (int e = 0; e < 4; e++) o[d][e] = 0.f;
+    float m_i[2] = {-INFINITY, -INFINITY}, l_i[2] = {0.f, 0.f};
+    const bool my_row[2] = {g < n_here, g + 8 < n_here};
+
+    for (int p = p_first; p <= p_last; p++) {
+        const int stage = (p - p_first) % NS;
+        cp_wait<NS - 1>();
+        __syncthreads();
+        if (p == p_first) {
             #pragma unroll
-            for (int x = 0; x < DPL; x++) {
-                const float o_o = __shfl_xor_sync(0xffffffffu, o[hh][x], off);
-                o[hh][x] = o[hh][x] * a + o_o * bsc;
+            for (int ks = 0; ks < HD / 16; ks++)
+                ldsm4(qf[ks], Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * LD + ks * 16 + (lane >> 4) * 8);
+        }
+        const bf16* ks_ = Ks + (stage * PAGE + warp * 16) * LD;
+        const bf16* vs_ = Vs + (stage * PAGE + warp * 16) * LD;
+        float s[2][4];
+        #pragma unroll
+        for (int n = 0; n < 2; n++)
+            #pragma unroll
+            for (int e = 0; e < 4; e++) s[n][e] = 0.f;
+        #pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) {
+            uint32_t bfr[4];
+            ldsm4(bfr, ks_ + ((lane & 7) + (lane >> 4) * 8) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
+            mma(s[0], qf[ks], bfr[0], bfr[1]);
+            mma(s[1], qf[ks], bfr[2], bfr[3]);
+        }
+        const int jbase = p * PAGE + warp * 16 + 2 * t;
+        float mx[2] = {-INFINITY, -INFINITY};
+        #pragma unroll
+        for (int n = 0; n < 2; n++)
+            #pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int r = e >> 1, j = jbase + n * 8 + (e & 1);
+                const bool ok = my_row[r] && j <= pos && j >= j0;
+                const float v = ok ? s[n][e] * scale_log2e : -INFINITY;
+                s[n][e] = v;
+                mx[r] = fmaxf(mx[r], v);
             }
-            m[hh] = m_n;
-        }
-    }
-    __shared__ float sm_o[4][GC][HD];
-    __shared__ float sm_ml[4][GC][2];
-    if (grp == 0) {
+        float alpha[2];
         #pragma unroll
-        for (int hh = 0; hh < GC; hh++) {
-            #pragma unroll
-            for (int x = 0; x < DPL; x++) sm_o[warp][hh][li * DPL + x] = o[hh][x];
-            if (li == 0) { sm_ml[warp][hh][0] = m[hh]; sm_ml[warp][hh][1] = l[hh]; }
+        for (int r = 0; r < 2; r++) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m_i[r], mx[r]);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            alpha[r] = exp2f(m_i[r] - m_use);
+            m_i[r] = m_new;
+            mx[r] = m_use;
         }
+        float rs[2] = {0.f, 0.f};
+        #pragma unroll
+        for (int n = 0; n < 2; n++)
+            #pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float pv = exp2f(s[n][e] - mx[e >> 1]);
+                s[n][e] = pv;
+                rs[e >> 1] += pv;
+            }
+        #pragma unroll
+        for (int r = 0; r < 2; r++) l_i[r] = l_i[r] * alpha[r] + rs[r];
+        #pragma unroll
+        for (int d = 0; d < HD / 8; d++) {
+            o[d][0] *= alpha[0]; o[d][1] *= alpha[0]; o[d][2] *= alpha[1]; o[d][3] *= alpha[1];
+        }
+        uint32_t pa[4];
+        pa[0] = pack_bf16(s[0][0], s[0][1]);
+        pa[1] = pack_bf16(s[0][2], s[0][3]);
+        pa[2] = pack_bf16(s[1][0], s[1][1]);
+        pa[3] = pack_bf16(s[1][2], s[1][3]);
+        #pragma unroll
+        for (int dp = 0; dp < HD / 16; dp++) {
+            uint32_t bfr[4];
+            ldsm4t(bfr, vs_ + ((lane & 7) + ((lane >> 3) & 1) * 8) * LD + dp * 16 + (lane >> 4) * 8);
+            mma(o[2 * dp], pa, bfr[0], bfr[1]);
+            mma(o[2 * dp + 1], pa, bfr[2], bfr[3]);
+        }
+        __syncthreads();                                            // everyone is done with this stage
+        if (p + NS <= p_last) load_page(stage, p + NS);
+        cp_commit();
+    }
+    cp_wait<0>();
+    #pragma unroll
+    for (int r = 0; r < 2; r++) {
+        l_i[r] += __shfl_xor_sync(0xffffffffu, l_i[r], 1);
+        l_i[r] += __shfl_xor_sync(0xffffffffu, l_i[r], 2);
+    }
+    // the four warps' partial results, merged in warp order (the K/V ring is free now)
+    float* sm_o = (float*)Ks;                         // [4][16][HD]
+    float* sm_ml = sm_o + 4 * 16 * HD;                // [4][16][2]
+    #pragma unroll
+    for (int r = 0; r < 2; r++) {
+        const int row = g + 8 * r;
+        #pragma unroll
+        for (int d = 0; d < HD / 8; d++) {
+            sm_o[(warp * 16 + row) * HD + d * 8 + 2 * t] = o[d][2 * r];
+            sm_o[(warp * 16 + row) * HD + d * 8 + 2 * t + 1] = o[d][2 * r + 1];
+        }
+        if (t == 0) { sm_ml[(warp * 16 + row) * 2] = m_i[r]; sm_ml[(warp * 16 + row) * 2 + 1] = l_i[r]; }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < n_heads_here * HD; idx += 128) {
+    for (int idx = threadIdx.x; idx < n_here * HD; idx += 128) {
         const int hh = idx / HD, x = idx % HD;
         float mm = -INFINITY;
         #pragma unroll
-        for (int w = 0; w < 4; w++) mm = fmaxf(mm, sm_ml[w][hh][0]);
+        for (int w = 0; w < 4; w++) mm = fmaxf(mm, sm_ml[(w * 16 + hh) * 2]);
         const float m_use = mm == -INFINITY ? 0.f : mm;
         float acc = 0.f, ll = 0.f;
         #pragma unroll
         for (int w = 0; w < 4; w++) {
-            const float a = exp2f(sm_ml[w][hh][0] - m_use);
-            acc += sm_o[w][hh][x] * a;
-            ll += sm_ml[w][hh][1] * a;
+            const float a = exp2f(sm_ml[(w * 16 + hh) * 2] - m_use);
+            acc += sm_o[(w * 16 + hh) * HD + x] * a;
+            ll += sm_ml[(w * 16 + hh) * 2 + 1] * a;
         }
         const size_t slot = ((size_t)b * nh + h0 + hh) * n_splits + split;
         part_o[slot * HD + x] = acc;
@@ -411,7 +427,6 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
 }  // namespace
 
 IK_EXPORT int ik_attn_head_dim() { return HD; }
-IK_EXPORT int ik_attn_heads_per_block() { return GC; }
 
 IK_EXPORT int ik_attn_prefill(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_seqlens,
                               const int* kv_lens, const int* table, int table_stride, int B, int max_new, int nh,
@@ -442,13 +457,27 @@ IK_EXPORT int ik_attn_decode(const void* q, const void* k_pages, const void* v_p
     if (B <= 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size != PAGE || chunk_pages <= 0 || n_splits <= 0 ||
         n_splits > 65535)
         return IK_BAD_ARGUMENT;
-    const int G = nh / nkv, n_hc = (G + GC - 1) / GC;
+    const int G = nh / nkv, n_hc = (G + 15) / 16;
     if ((long long)nkv * n_hc > 65535) return IK_BAD_ARGUMENT;
     dim3 grid(B, nkv * n_hc, n_splits);
-    attn_decode_kernel<<<grid, 128, 0, stream>>>((const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, part_o,
-                                                 part_ml, kv_lens, table, table_stride, nh, nkv,
-                                                 scale * 1.4426950408889634f, window, n_pages, chunk_pages, n_splits,
-                                                 status);
+    // as many ring stages as fit ~105 KB (two blocks per SM), at least 2, at most 4
+    const size_t q_bytes = (size_t)16 * LD * sizeof(bf16), stage_bytes = (size_t)2 * PAGE * LD * sizeof(bf16);
+    int ns = (int)((105 * 1024 - q_bytes) / stage_bytes);
+    ns = ns < 2 ? 2 : ns > 4 ? 4 : ns;
+    const size_t smem = q_bytes + ns * stage_bytes;
+#define IK_DEC(NS_)                                                                                                  \
+    {                                                                                                                \
+        auto kern = attn_decode_kernel<NS_>;                                                                         \
+        if (smem > 48 * 1024) {                                                                                      \
+            cudaError_t e0 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+            if (e0 != cudaSuccess) return (int)e0;                                                                   \
+        }                                                                                                            \
+        kern<<<grid, 128, smem, stream>>>((const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, part_o, part_ml, \
+                                          kv_lens, table, table_stride, nh, nkv, scale * 1.4426950408889634f, window, \
+                                          n_pages, chunk_pages, n_splits, status);                                   \
+    }
+    if (ns == 2) IK_DEC(2) else if (ns == 3) IK_DEC(3) else IK_DEC(4)
+#undef IK_DEC
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     dim3 grid2(B, nh);

@@ -1,8 +1,8 @@
 """Attention kernels of the bfloat16 path: one compiled module per head size.
 
-``attention_bf16.cu`` is specialised at compile time for a head size and for the number
-of query heads a decode block serves; the module for the sizes a model has is compiled
-the first time that model runs a step (a few seconds) and kept beside the core library.
+``attention_bf16.cu`` is specialised at compile time for a head size; the module for the
+size a model has is compiled the first time that model runs a step (a few seconds) and kept
+beside the core library.
 """
 from __future__ import annotations
 
@@ -15,37 +15,20 @@ from . import build
 from .ops import KernelError, _check, _ptr, _stream
 
 _vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
-_modules: Dict[Tuple[int, int], ctypes.CDLL] = {}
+_modules: Dict[int, ctypes.CDLL] = {}
 
 DECODE_CHUNK_PAGES = 4        # a decode block covers 4 pages = 256 keys; chunks start at multiples of that
-
-
-def lanes_per_key(head_dim: int) -> int:
-    for l in (16, 8, 4, 2, 1):
-        if head_dim % (8 * l) == 0 and head_dim // l <= 32:
-            return l
-    for l in (16, 8, 4, 2, 1):
-        if head_dim % (8 * l) == 0:
-            return l
-    return 1
-
-
-def heads_per_block(head_dim: int, group: int) -> int:
-    dpl = head_dim // lanes_per_key(head_dim)
-    cap = 4 if dpl <= 16 else 2 if dpl <= 32 else 1
-    return max(1, min(group, cap))
 
 
 def supported(head_dim: int) -> bool:
     return head_dim % 16 == 0 and 16 <= head_dim <= 256
 
 
-def module(head_dim: int, gc: int) -> ctypes.CDLL:
-    key = (head_dim, gc)
+def module(head_dim: int) -> ctypes.CDLL:
+    key = head_dim
     m = _modules.get(key)
     if m is None:
-        m = build.load_library(f"ithaca_attn_hd{head_dim}_g{gc}", ["attention_bf16.cu"],
-                               defines=[f"IK_HD={head_dim}", f"IK_GC={gc}"])
+        m = build.load_library(f"ithaca_attn_hd{head_dim}", ["attention_bf16.cu"], defines=[f"IK_HD={head_dim}"])
         m.ik_attn_prefill.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp]
         m.ik_attn_prefill.restype = _i
         m.ik_attn_decode.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _i, _i, _i,
@@ -61,7 +44,7 @@ def prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, cu_se
             kv_lens: torch.Tensor, table: torch.Tensor, n_seqs: int, max_new: int, n_heads: int, scale: float,
             window: int, status: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
     n_pages, nkv, page_size, hd = k_pages.shape
-    m = module(hd, heads_per_block(hd, n_heads // nkv))
+    m = module(hd)
     if out is None:
         out = torch.empty_like(q)
     _check(m.ik_attn_prefill(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(cu_seqlens), _ptr(kv_lens),
@@ -76,7 +59,7 @@ def decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, kv_len
     """``kv_len_bound``: no sequence of the step is longer than this (it sizes the grid and the
     scratch for the partial results; blocks beyond a sequence's length return at once)."""
     n_pages, nkv, page_size, hd = k_pages.shape
-    m = module(hd, heads_per_block(hd, n_heads // nkv))
+    m = module(hd)
     n_splits = max(1, -(-kv_len_bound // (chunk_pages * page_size)))
     part_o = torch.empty((n_seqs, n_heads, n_splits, hd), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((n_seqs, n_heads, n_splits, 2), dtype=torch.float32, device=q.device)
