@@ -70,6 +70,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
                     bf16* __restrict__ out, const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,
                     const int* __restrict__ table, int table_stride, int nh, int nkv, float scale_log2e, int window,
                     int n_pages, int* status) {
+    ik_pdl_launch_dependents();
+    ik_pdl_wait();
     constexpr int BM = 16 * NW, THREADS = 32 * NW, CH = HD / 8;          // CH: 16-byte chunks per row
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = (bf16*)smem_raw;                      // [BM][LD]
@@ -233,6 +235,8 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
                    float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ kv_lens,
                    const int* __restrict__ table, int table_stride, int nh, int nkv, float scale_log2e, int window,
                    int n_pages, int chunk_pages, int n_splits, int* status) {
+    ik_pdl_launch_dependents();
+    ik_pdl_wait();
     constexpr int CH = HD / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = (bf16*)smem_raw;                      // [16][LD]
@@ -405,6 +409,8 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, const int* __restrict__ kv_lens, int nh, int window,
                                     int chunk_pages, int n_splits) {
+    ik_pdl_launch_dependents();
+    ik_pdl_wait();
     const int b = blockIdx.x, h = blockIdx.y;
     const int len = kv_lens[b], pos = len - 1;
     const int j0 = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
@@ -442,9 +448,9 @@ IK_EXPORT int ik_attn_prefill(const void* q, const void* k_pages, const void* v_
         if (e != cudaSuccess) return (int)e;
     }
     dim3 grid((max_new + BM - 1) / BM, nh, B);
-    kern<<<grid, 32 * NW, smem, stream>>>((const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out,
+    IK_RETURN_IF_ERROR(ik_launch(kern, grid, 32 * NW, smem, stream, (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out,
                                           cu_seqlens, kv_lens, table, table_stride, nh, nkv,
-                                          scale * 1.4426950408889634f, window, n_pages, status);
+                                          scale * 1.4426950408889634f, window, n_pages, status));
     IK_LAUNCH_STATUS();
 }
 
@@ -472,16 +478,16 @@ IK_EXPORT int ik_attn_decode(const void* q, const void* k_pages, const void* v_p
             cudaError_t e0 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
             if (e0 != cudaSuccess) return (int)e0;                                                                   \
         }                                                                                                            \
-        kern<<<grid, 128, smem, stream>>>((const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, part_o, part_ml, \
+        IK_RETURN_IF_ERROR(ik_launch(kern, grid, 128, smem, stream, (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, part_o, part_ml, \
                                           kv_lens, table, table_stride, nh, nkv, scale * 1.4426950408889634f, window, \
-                                          n_pages, chunk_pages, n_splits, status);                                   \
+                                          n_pages, chunk_pages, n_splits, status));                                   \
     }
     if (ns == 2) IK_DEC(2) else if (ns == 3) IK_DEC(3) else IK_DEC(4)
 #undef IK_DEC
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     dim3 grid2(B, nh);
-    attn_combine_kernel<<<grid2, HD < 128 ? HD : 128, 0, stream>>>(part_o, part_ml, (bf16*)out, kv_lens, nh, window,
-                                                                    chunk_pages, n_splits);
+    IK_RETURN_IF_ERROR(ik_launch(attn_combine_kernel, grid2, HD < 128 ? HD : 128, 0, stream, part_o, part_ml, (bf16*)out, kv_lens, nh, window,
+                                                                    chunk_pages, n_splits));
     IK_LAUNCH_STATUS();
 }

@@ -21,6 +21,8 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pages, 
                       TO* __restrict__ out, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                       const int* __restrict__ table, int table_stride, int nh, int nkv, int hd, float scale,
                       int window, int page_size, int n_pages, int* status) {
+    ik_pdl_launch_dependents();
+    ik_pdl_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     size_t* row = (size_t*)smem;              // [TILE] element offset of key j's row in the pages
     float* qs = (float*)(row + TILE);         // [hd]
@@ -103,8 +105,8 @@ IK_EXPORT int ik_attention_simt(const void* q, int q_dtype, const void* k_pages,
     dim3 grid(T, nh);
     const size_t smem = (size_t)(hd + TILE + 32) * sizeof(float) + TILE * sizeof(size_t);
 #define IK_ATT(TQ, TC)                                                                                                \
-    attention_simt_kernel<TQ, TC, TQ><<<grid, TILE, smem, stream>>>((const TQ*)q, (const TC*)k_pages, (const TC*)v_pages, \
-        (TQ*)out, token_seq, token_pos, table, table_stride, nh, nkv, hd, scale, window, page_size, n_pages, status)
+    IK_RETURN_IF_ERROR(ik_launch(attention_simt_kernel<TQ, TC, TQ>, grid, TILE, smem, stream, (const TQ*)q, (const TC*)k_pages, (const TC*)v_pages, \
+        (TQ*)out, token_seq, token_pos, table, table_stride, nh, nkv, hd, scale, window, page_size, n_pages, status))
     if (q_dtype == IK_F32 && cache_dtype == IK_F32) IK_ATT(float, float);
     else if (q_dtype == IK_BF16 && cache_dtype == IK_BF16) IK_ATT(__nv_bfloat16, __nv_bfloat16);
     else if (q_dtype == IK_F32 && cache_dtype == IK_BF16) IK_ATT(float, __nv_bfloat16);

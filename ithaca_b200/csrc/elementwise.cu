@@ -10,6 +10,8 @@
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ out,
                              int d, int V, float scale, int* status) {
+    ik_pdl_launch_dependents();
+    ik_pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < V;
@@ -24,9 +26,9 @@ IK_EXPORT int ik_embed(const int* ids, const void* table, int table_dtype, float
     if (T < 0 || d <= 0 || V <= 0) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
     if (table_dtype == IK_F32)
-        embed_kernel<float><<<T, 256, 0, stream>>>(ids, (const float*)table, out, d, V, scale, status);
+        IK_RETURN_IF_ERROR(ik_launch(embed_kernel<float>, T, 256, 0, stream, ids, (const float*)table, out, d, V, scale, status));
     else if (table_dtype == IK_BF16)
-        embed_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, d, V, scale, status);
+        IK_RETURN_IF_ERROR(ik_launch(embed_kernel<__nv_bfloat16>, T, 256, 0, stream, ids, (const __nv_bfloat16*)table, out, d, V, scale, status));
     else
         return IK_BAD_ARGUMENT;
     IK_LAUNCH_STATUS();
@@ -38,6 +40,8 @@ IK_EXPORT int ik_embed(const int* ids, const void* table, int table_dtype, float
 template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows_in,
                                const float* __restrict__ w, TO* __restrict__ out, int d, float eps) {
+    ik_pdl_launch_dependents();
+    ik_pdl_wait();
     __shared__ float red[32];
     const int r = blockIdx.x;
     const float* a = x + (size_t)(rows_in ? rows_in[r] : r) * d;
@@ -54,9 +58,9 @@ IK_EXPORT int ik_rmsnorm(const float* x, const int* rows_in, const float* w, voi
     if (rows < 0 || d <= 0) return IK_BAD_ARGUMENT;
     if (rows == 0) return IK_OK;
     if (out_dtype == IK_F32)
-        rmsnorm_kernel<float><<<rows, 256, 0, stream>>>(x, rows_in, w, (float*)out, d, eps);
+        IK_RETURN_IF_ERROR(ik_launch(rmsnorm_kernel<float>, rows, 256, 0, stream, x, rows_in, w, (float*)out, d, eps));
     else if (out_dtype == IK_BF16)
-        rmsnorm_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>(x, rows_in, w, (__nv_bfloat16*)out, d, eps);
+        IK_RETURN_IF_ERROR(ik_launch(rmsnorm_kernel<__nv_bfloat16>, rows, 256, 0, stream, x, rows_in, w, (__nv_bfloat16*)out, d, eps));
     else
         return IK_BAD_ARGUMENT;
     IK_LAUNCH_STATUS();
@@ -66,6 +70,8 @@ IK_EXPORT int ik_rmsnorm(const float* x, const int* rows_in, const float* w, voi
 // in: [T, 2*ff] float, gate in columns [0, ff), up in [ff, 2ff).  out[t, j] = silu(g) * u.
 template <typename TO>
 __global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out, int ff, size_t total) {
+    ik_pdl_launch_dependents();
+    ik_pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / ff;
         const int j = (int)(idx - t * ff);
@@ -80,9 +86,9 @@ IK_EXPORT int ik_swiglu(const float* gate_up, void* out, int out_dtype, int T, i
     const size_t total = (size_t)T * ff;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     if (out_dtype == IK_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>(gate_up, (float*)out, ff, total);
+        IK_RETURN_IF_ERROR(ik_launch(swiglu_kernel<float>, blocks, 256, 0, stream, gate_up, (float*)out, ff, total));
     else if (out_dtype == IK_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(gate_up, (__nv_bfloat16*)out, ff, total);
+        IK_RETURN_IF_ERROR(ik_launch(swiglu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, gate_up, (__nv_bfloat16*)out, ff, total));
     else
         return IK_BAD_ARGUMENT;
     IK_LAUNCH_STATUS();
@@ -105,6 +111,8 @@ __global__ void rope_append_kernel(const float* __restrict__ qkv, TQ* __restrict
                                    const int* __restrict__ token_pos, const int* __restrict__ table, int table_stride,
                                    const float* __restrict__ inv_freq, int nh, int nkv, int hd, int rot, int pairing,
                                    int page_size, int n_pages, int write_cache, int* status) {
+    ik_pdl_launch_dependents();
+    ik_pdl_wait();
     const int t = blockIdx.x, head = blockIdx.y;
     const int pos = token_pos[t];
     const float* src = qkv + (size_t)t * (nh + 2 * nkv) * hd + (size_t)head * hd;
@@ -152,8 +160,8 @@ IK_EXPORT int ik_rope_append(const float* qkv, void* q_out, int q_dtype, void* k
     dim3 grid(T, nh + 2 * nkv);
     const int threads = 64;
 #define IK_ROPE(TQ, TC)                                                                                             \
-    rope_append_kernel<TQ, TC><<<grid, threads, 0, stream>>>(qkv, (TQ*)q_out, (TC*)k_pages, (TC*)v_pages, token_seq, \
-        token_pos, table, table_stride, inv_freq, nh, nkv, hd, rot, pairing, page_size, n_pages, write_cache, status)
+    IK_RETURN_IF_ERROR(ik_launch(rope_append_kernel<TQ, TC>, grid, threads, 0, stream, qkv, (TQ*)q_out, (TC*)k_pages, (TC*)v_pages, token_seq, \
+        token_pos, table, table_stride, inv_freq, nh, nkv, hd, rot, pairing, page_size, n_pages, write_cache, status))
     if (q_dtype == IK_F32 && cache_dtype == IK_F32) IK_ROPE(float, float);
     else if (q_dtype == IK_BF16 && cache_dtype == IK_BF16) IK_ROPE(__nv_bfloat16, __nv_bfloat16);
     else if (q_dtype == IK_F32 && cache_dtype == IK_BF16) IK_ROPE(float, __nv_bfloat16);

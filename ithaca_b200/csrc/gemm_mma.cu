@@ -3,7 +3,7 @@
 //
 // Two kernels.
 //  * skinny (M <= 64, decode): weights are the 16-row operand, tokens the 8-column operand, so a
-//    handful of tokens costs no wasted tensor work.  A block owns 16 or 32 weight rows; its 8
+//    handful of tokens costs no wasted tensor work.  A block owns 16 weight rows; its 8
 //    warps split K between them and their partial sums are added in warp order at the end.
 //    Each thread streams 16 contiguous bytes of a weight row per load, straight from global
 //    memory to registers: weights are read exactly once.
@@ -44,34 +44,35 @@ __device__ __forceinline__ void store_out(__nv_bfloat16* Y, size_t o, float v, i
 }
 
 // ------------------------------------------------------------------------------------------ skinny
-// NT: 8-token column tiles (M <= 8 NT).  RF: 16-row fragments per block (R = 16 RF rows).
-template <int NT, int RF, typename TY>
+// NT: 8-token column tiles (M <= 8 NT).  A block owns 16 weight rows; each of its 8 warps takes
+// every 8th group of U 64-wide K blocks, loads all of the group's weights (16 bytes per thread
+// per load, 4 U loads in flight per thread) and tokens, then multiplies.  U trades registers
+// (blocks per SM) for bytes in flight; the host picks it per shape.
+template <int NT, int U, typename TY>
 __global__ void __launch_bounds__(256)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, TY* __restrict__ Y,
                    int M, int N, int K, int ldx, int ldw, int ldy, int accumulate) {
-    constexpr int R = 16 * RF, COLS = 8 * NT;
+    constexpr int R = 16, COLS = 8 * NT;
     extern __shared__ float red[];                       // [8 warps][R][COLS]
+    ik_pdl_launch_dependents();
+    ik_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * R;
 
-    float acc[RF][NT][4];
+    float acc[NT][4];
     #pragma unroll
-    for (int r = 0; r < RF; r++)
+    for (int n = 0; n < NT; n++)
         #pragma unroll
-        for (int n = 0; n < NT; n++)
-            #pragma unroll
-            for (int i = 0; i < 4; i++) acc[r][n][i] = 0.f;
+        for (int i = 0; i < 4; i++) acc[n][i] = 0.f;
 
-    const __nv_bfloat16* wrow[RF][2];
-    bool wok[RF][2];
+    const __nv_bfloat16* wrow[2];
+    bool wok[2];
     #pragma unroll
-    for (int r = 0; r < RF; r++)
-        #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const int row = n0 + r * 16 + h * 8 + g;
-            wok[r][h] = row < N;
-            wrow[r][h] = W + (size_t)(wok[r][h] ? row : 0) * ldw;
-        }
+    for (int h = 0; h < 2; h++) {
+        const int row = n0 + h * 8 + g;
+        wok[h] = row < N;
+        wrow[h] = W + (size_t)(wok[h] ? row : 0) * ldw;
+    }
     const __nv_bfloat16* xrow[NT];
     bool xok[NT];
     #pragma unroll
@@ -83,41 +84,39 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
 
     const uint4 zero = make_uint4(0, 0, 0, 0);
     const int nblk = (K + 63) / 64;                       // blocks of 64 k = two 32-k chunks, 128 bytes of a row
-    for (int blk = warp; blk < nblk; blk += 8) {
-        uint4 a[2][RF][2], b[2][NT];
+    for (int blk0 = warp * U; blk0 < nblk; blk0 += 8 * U) {
+        uint4 a[U][2][2], b[U][2][NT];
         #pragma unroll
-        for (int c = 0; c < 2; c++) {
-            const int k = blk * 64 + c * 32 + t * 8;
-            const bool kok = k < K;                       // K % 8 == 0: the whole 8 are inside
+        for (int u = 0; u < U; u++)
             #pragma unroll
-            for (int r = 0; r < RF; r++)
+            for (int c = 0; c < 2; c++) {
+                const int k = (blk0 + u) * 64 + c * 32 + t * 8;
+                const bool kok = k < K;                   // K % 8 == 0: the whole 8 are inside
                 #pragma unroll
-                for (int h = 0; h < 2; h++) a[c][r][h] = (kok && wok[r][h]) ? ld_stream(wrow[r][h] + k) : zero;
-            #pragma unroll
-            for (int n = 0; n < NT; n++) b[c][n] = (kok && xok[n]) ? __ldg((const uint4*)(xrow[n] + k)) : zero;
-        }
+                for (int h = 0; h < 2; h++) a[u][c][h] = (kok && wok[h]) ? ld_stream(wrow[h] + k) : zero;
+                #pragma unroll
+                for (int n = 0; n < NT; n++) b[u][c][n] = (kok && xok[n]) ? __ldg((const uint4*)(xrow[n] + k)) : zero;
+            }
         #pragma unroll
-        for (int c = 0; c < 2; c++)
+        for (int u = 0; u < U; u++)
             #pragma unroll
-            for (int r = 0; r < RF; r++)
+            for (int c = 0; c < 2; c++)
                 #pragma unroll
                 for (int n = 0; n < NT; n++) {
-                    mma_bf16(acc[r][n], a[c][r][0].x, a[c][r][1].x, a[c][r][0].y, a[c][r][1].y, b[c][n].x, b[c][n].y);
-                    mma_bf16(acc[r][n], a[c][r][0].z, a[c][r][1].z, a[c][r][0].w, a[c][r][1].w, b[c][n].z, b[c][n].w);
+                    mma_bf16(acc[n], a[u][c][0].x, a[u][c][1].x, a[u][c][0].y, a[u][c][1].y, b[u][c][n].x, b[u][c][n].y);
+                    mma_bf16(acc[n], a[u][c][0].z, a[u][c][1].z, a[u][c][0].w, a[u][c][1].w, b[u][c][n].z, b[u][c][n].w);
                 }
     }
     // partial sums of the 8 warps, added in warp order
     float* mine = red + (size_t)warp * R * COLS;
     #pragma unroll
-    for (int r = 0; r < RF; r++)
-        #pragma unroll
-        for (int n = 0; n < NT; n++) {
-            const int row = r * 16 + g, col = n * 8 + 2 * t;
-            mine[(row) * COLS + col] = acc[r][n][0];
-            mine[(row) * COLS + col + 1] = acc[r][n][1];
-            mine[(row + 8) * COLS + col] = acc[r][n][2];
-            mine[(row + 8) * COLS + col + 1] = acc[r][n][3];
-        }
+    for (int n = 0; n < NT; n++) {
+        const int col = n * 8 + 2 * t;
+        mine[g * COLS + col] = acc[n][0];
+        mine[g * COLS + col + 1] = acc[n][1];
+        mine[(g + 8) * COLS + col] = acc[n][2];
+        mine[(g + 8) * COLS + col + 1] = acc[n][3];
+    }
     __syncthreads();
     for (int idx = threadIdx.x; idx < R * COLS; idx += 256) {
         const int m = idx / R, row = idx % R;             // consecutive threads: consecutive features
@@ -129,19 +128,23 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
     }
 }
 
-template <int NT, int RF, typename TY>
+template <int NT, int U, typename TY>
 int launch_skinny(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
                   int accumulate, cudaStream_t stream) {
-    constexpr int R = 16 * RF;
+    constexpr int R = 16;
     const size_t smem = (size_t)8 * R * 8 * NT * sizeof(float);
-    auto kern = gemm_skinny_kernel<NT, RF, TY>;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-    }
-    kern<<<(N + R - 1) / R, 256, smem, stream>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (TY*)Y, M, N, K, ldx,
-                                                  ldw, ldy, accumulate);
+    auto kern = gemm_skinny_kernel<NT, U, TY>;
+    IK_RETURN_IF_ERROR(ik_launch(kern, (N + R - 1) / R, 256, smem, stream, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W,
+                                 (TY*)Y, M, N, K, ldx, ldw, ldy, accumulate));
     IK_LAUNCH_STATUS();
+}
+
+// The deeper unroll (more bytes in flight, 2 blocks per SM instead of 3) pays unless the grid then fills
+// its last wave of blocks badly.  Depends on N only, so a row's summation order does not depend on M.
+bool deep_unroll_pays(int N) {
+    const int blocks = (N + 15) / 16, slots = 2 * 148;
+    const int waves = (blocks + slots - 1) / slots;
+    return (double)blocks / ((double)waves * slots) >= 0.8;
 }
 
 // ------------------------------------------------------------------------------------------ tiled
@@ -158,6 +161,8 @@ __global__ void __launch_bounds__(256)
 gemm_tiled_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, TY* __restrict__ Y,
                   int M, int N, int K, int ldx, int ldw, int ldy, int accumulate) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    ik_pdl_launch_dependents();
+    ik_pdl_wait();
     __nv_bfloat16* xs = (__nv_bfloat16*)smem_raw;                         // [STAGES][TBM][TBK]
     __nv_bfloat16* ws = xs + (size_t)STAGES * TBM * TBK;                  // [STAGES][TBN][TBK]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -236,8 +241,8 @@ int launch_tiled(const void* X, const void* W, void* Y, int M, int N, int K, int
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((N + TBN - 1) / TBN, (M + TBM - 1) / TBM);
-    kern<<<grid, 256, smem, stream>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (TY*)Y, M, N, K, ldx, ldw, ldy,
-                                      accumulate);
+    IK_RETURN_IF_ERROR(ik_launch(kern, grid, 256, smem, stream, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (TY*)Y, M, N, K, ldx, ldw, ldy,
+                                      accumulate));
     IK_LAUNCH_STATUS();
 }
 
@@ -256,15 +261,14 @@ IK_EXPORT int ik_gemm_bf16_mma(const void* X, const void* W, void* Y, int y_dtyp
     if (M == 0) return IK_OK;
     const bool skinny = kind == 1 || (kind == 0 && M <= 64);
     if (skinny && M > 64) return IK_UNSUPPORTED;
-#define IK_SK(NT, RF)                                                                                          \
-    return y_dtype == IK_F32 ? launch_skinny<NT, RF, float>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, stream) \
-                             : launch_skinny<NT, RF, __nv_bfloat16>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, stream)
+#define IK_SK(NT, U)                                                                                           \
+    return y_dtype == IK_F32 ? launch_skinny<NT, U, float>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, stream) \
+                             : launch_skinny<NT, U, __nv_bfloat16>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, stream)
     if (skinny) {
-        // 32 rows a block when that still gives every SM two blocks, else 16 rows a block
-        const bool wide = (N + 31) / 32 >= 2 * 148;
-        if (M <= 8) { if (wide) { IK_SK(1, 2); } IK_SK(1, 1); }
-        if (M <= 16) { if (wide) { IK_SK(2, 2); } IK_SK(2, 1); }
-        if (M <= 32) { if (wide) { IK_SK(4, 2); } IK_SK(4, 1); }
+        const bool deep = deep_unroll_pays(N);
+        if (M <= 8) { if (deep) { IK_SK(1, 4); } IK_SK(1, 2); }
+        if (M <= 16) { if (deep) { IK_SK(2, 2); } IK_SK(2, 1); }
+        if (M <= 32) { IK_SK(4, 1); }
         IK_SK(8, 1);
     }
 #undef IK_SK

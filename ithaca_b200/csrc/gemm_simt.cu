@@ -15,6 +15,8 @@ template <typename TX, typename TW, typename TY>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TX* __restrict__ X, const TW* __restrict__ W, TY* __restrict__ Y, int M, int N, int K,
                  int ldx, int ldw, int ldy, int accumulate) {
+    ik_pdl_launch_dependents();
+    ik_pdl_wait();
     __shared__ float xs[BK][BM + 1];
     __shared__ float ws[BK][BN + 1];
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -70,8 +72,8 @@ template <typename TX, typename TW, typename TY>
 int launch(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy, int accumulate,
            cudaStream_t stream) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_simt_kernel<TX, TW, TY><<<grid, 256, 0, stream>>>((const TX*)X, (const TW*)W, (TY*)Y, M, N, K, ldx, ldw, ldy,
-                                                            accumulate);
+    IK_RETURN_IF_ERROR(ik_launch(gemm_simt_kernel<TX, TW, TY>, grid, 256, 0, stream, (const TX*)X, (const TW*)W, (TY*)Y, M, N, K, ldx, ldw, ldy,
+                                                            accumulate));
     IK_LAUNCH_STATUS();
 }
 

@@ -6,14 +6,15 @@
 // and decode alike: the epilogue then writes, for each token, 32 consecutive features per warp
 // instruction (coalesced), and a handful of decode tokens wastes no tensor work.
 //
-// One block computes one 128 x BN tile (optionally one slice of K):
+// A block computes 128 x BN tiles (optionally one slice of K each), one after another:
 //   warp 0      one lane issues the TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the
 //               128 x 64 weight tile and the BN x 64 token tile of each K step into a ring of
 //               shared-memory stages; completion is counted on the stage's "full" mbarrier.
-//   warp 1      allocates TMEM; one lane issues four tcgen05.mma (K = 16 each) per stage and
-//               commits them to the stage's "empty" mbarrier; after the last stage it commits to
-//               the "accumulator ready" mbarrier.  Frees TMEM at the end.
-//   warps 2..5  read the accumulator with tcgen05.ld (each warp its 32 lanes) and store it.
+//   warp 1      allocates TMEM (two accumulators); one lane issues four tcgen05.mma (K = 16 each)
+//               per stage and commits them to the stage's "empty" mbarrier; after a tile's last
+//               stage it commits to that accumulator's "full" mbarrier.  Frees TMEM at the end.
+//   warps 2..5  read a full accumulator with tcgen05.ld (each warp its 32 lanes), store it, and
+//               hand it back ("empty") while the MMA warp is already filling the other one.
 // Tails in M, N and K are zero-filled by TMA and masked in the epilogue.  No multicast, no
 // clusters.
 //
@@ -122,37 +123,48 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 template <int BN> struct Cfg {
     static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE = A_BYTES + B_BYTES;
     static constexpr int STAGES = (200 * 1024 / STAGE) > 8 ? 8 : (200 * 1024 / STAGE);
-    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr int ACC_COLS = BN < 32 ? 32 : BN;           // TMEM columns of one accumulator
+    static constexpr int TMEM_COLS = 2 * ACC_COLS;               // two accumulators: one is drained while the other fills
     static constexpr int SMEM = STAGES * STAGE + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+
 // map_w: [N rows, K] box {64, 128};  map_x: [M rows, K] box {64, BN}.
 // out: Y (float or bf16) when partial == nullptr, else partial sums [splits][M][N] float.
+//
+// Persistent: the grid has at most one block per SM and every block walks the tiles
+// t = blockIdx.x, blockIdx.x + gridDim.x, ...  Tiles that share a weight tile are neighbours in
+// that order, so they run at the same time on different SMs and the weight tile is fetched from
+// HBM once.  The accumulator is double-buffered in TMEM: while the epilogue warps drain tile i,
+// the MMA warp already fills the other buffer with tile i + 1.
 template <int BN, typename TY>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     TY* __restrict__ Y, float* __restrict__ partial, int M, int N, int K, int ldy, int accumulate,
-                    int kb_per_split, int* status) {
+                    int kb_per_split, int n_splits, int* status) {
     typedef Cfg<BN> C;
     extern __shared__ unsigned char smem_raw[];
+    ik_pdl_launch_dependents();
     if (status && *(volatile int*)status == IK_STATUS_GEMM_TIMEOUT) return;     // an earlier block gave up
     unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = (uint64_t*)(tiles + C::STAGES * C::STAGE);
     uint64_t* empty = full + C::STAGES;
-    uint64_t* acc_ready = empty + C::STAGES;
-    uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+    uint64_t* acc_full = empty + C::STAGES;            // [2] accumulator written, ready to be drained
+    uint64_t* acc_empty = acc_full + 2;                // [2] accumulator drained, free to be overwritten
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BM;                    // first weight row (output feature)
-    const int m0 = blockIdx.y * BN;                    // first token
+    const int tiles_n = (N + BM - 1) / BM, tiles_m = (M + BN - 1) / BN;
+    const int total_tiles = tiles_n * tiles_m * n_splits;
     const int nkb_total = (K + BK - 1) / BK;
-    const int kb0 = blockIdx.z * kb_per_split;
-    const int nkb = min(kb_per_split, nkb_total - kb0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
-        mbar_init(acc_ready, 1);
+        for (int b = 0; b < 2; b++) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 128); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" :: "l"(&map_w) : "memory");
@@ -167,18 +179,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    ik_pdl_wait();
+
+    // tile t -> (K slice z, weight tile nt, token tile mt), token tile fastest
+    #define IK_TILE_COORDS(t)                                                   \
+        const int mt = (t) % tiles_m, nt = ((t) / tiles_m) % tiles_n, z = (t) / (tiles_m * tiles_n); \
+        const int n0 = nt * BM, m0 = mt * BN, kb0 = z * kb_per_split;           \
+        const int nkb = min(kb_per_split, nkb_total - kb0);
 
     if (warp == 0) {
         if (lane == 0) {
-            int armed = 0;
-            for (int i = 0; i < nkb; i++) {
-                const int s = i % C::STAGES;
-                if (!mbar_wait(empty + s, ((i / C::STAGES) & 1) ^ 1, abort_flag, status)) break;
-                unsigned char* a = tiles + s * C::STAGE;
-                mbar_expect_tx(full + s, C::STAGE);
-                tma_load_2d(a, &map_w, (kb0 + i) * BK, n0, full + s);
-                tma_load_2d(a + C::A_BYTES, &map_x, (kb0 + i) * BK, m0, full + s);
-                armed = i + 1;
+            int it = 0, armed = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                IK_TILE_COORDS(t)
+                (void)z;
+                for (int i = 0; i < nkb; i++, it++) {
+                    const int s = it % C::STAGES;
+                    if (!mbar_wait(empty + s, ((it / C::STAGES) & 1) ^ 1, abort_flag, status)) { ok = false; break; }
+                    unsigned char* a = tiles + s * C::STAGE;
+                    mbar_expect_tx(full + s, C::STAGE);
+                    tma_load_2d(a, &map_w, (kb0 + i) * BK, n0, full + s);
+                    tma_load_2d(a + C::A_BYTES, &map_x, (kb0 + i) * BK, m0, full + s);
+                    armed = it + 1;
+                }
             }
             if (*abort_flag) {
                 // leave no copy of this block in flight: wait (bounded) for the stages that were armed last
@@ -191,49 +215,72 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(BN);
+            int it = 0, lt = 0;
             bool ok = true;
-            for (int i = 0; i < nkb && ok; i++) {
-                const int s = i % C::STAGES;
-                ok = mbar_wait(full + s, (i / C::STAGES) & 1, abort_flag, status);
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, lt++) {
+                IK_TILE_COORDS(t)
+                (void)z; (void)n0; (void)m0; (void)kb0;
+                const int buf = lt & 1;
+                ok = mbar_wait(acc_empty + buf, ((lt >> 1) & 1) ^ 1, abort_flag, status);   // drained by the epilogue
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a = smem_u32(tiles + s * C::STAGE), b = a + C::A_BYTES;
-                #pragma unroll
-                for (int j = 0; j < BK / 16; j++)
-                    umma(tmem_base, umma_desc(a + j * 32), umma_desc(b + j * 32), idesc, (i | j) != 0);
-                umma_commit(empty + s);                 // the stage is free once these MMAs have read it
+                const uint32_t acc = tmem_base + buf * C::ACC_COLS;
+                for (int i = 0; i < nkb; i++, it++) {
+                    const int s = it % C::STAGES;
+                    ok = mbar_wait(full + s, (it / C::STAGES) & 1, abort_flag, status);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a = smem_u32(tiles + s * C::STAGE), b = a + C::A_BYTES;
+                    #pragma unroll
+                    for (int j = 0; j < BK / 16; j++)
+                        umma(acc, umma_desc(a + j * 32), umma_desc(b + j * 32), idesc, (i | j) != 0);
+                    umma_commit(empty + s);             // the stage is free once these MMAs have read it
+                }
+                if (ok) umma_commit(acc_full + buf);
             }
-            if (ok) umma_commit(acc_ready);
         }
     } else {
         // epilogue: warp w owns TMEM lanes 32 * (w % 4) .. + 31
         const int quarter = warp & 3;
-        const int feature = n0 + quarter * 32 + lane;
-        if (nkb > 0 && mbar_wait(acc_ready, 0, abort_flag, status)) {
+        int lt = 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, lt++) {
+            IK_TILE_COORDS(t)
+            (void)kb0; (void)nkb;
+            const int buf = lt & 1;
+            const int feature = n0 + quarter * 32 + lane;
+            if (!mbar_wait(acc_full + buf, (lt >> 1) & 1, abort_flag, status)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * C::ACC_COLS;
             #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 if (m0 + c0 >= M) break;
                 float v[16];
-                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c0, v);
+                tmem_ld16(acc + c0, v);
                 if (feature < N) {
-                    #pragma unroll
-                    for (int c = 0; c < 16; c++) {
-                        const int m = m0 + c0 + c;
-                        if (m >= M) break;
-                        if (partial) {
-                            partial[((size_t)blockIdx.z * M + m) * N + feature] = v[c];
-                        } else {
-                            const size_t o = (size_t)m * ldy + feature;
-                            float r = v[c];
-                            if (accumulate) r += ik_ld(Y, o);
-                            ik_st(Y, o, r);
+                    if (partial) {
+                        #pragma unroll
+                        for (int c = 0; c < 16; c++)
+                            if (m0 + c0 + c < M) partial[((size_t)z * M + m0 + c0 + c) * N + feature] = v[c];
+                    } else {
+                        if (accumulate) {
+                            float y[16];
+                            #pragma unroll
+                            for (int c = 0; c < 16; c++)
+                                y[c] = m0 + c0 + c < M ? ik_ld(Y, (size_t)(m0 + c0 + c) * ldy + feature) : 0.f;
+                            #pragma unroll
+                            for (int c = 0; c < 16; c++) v[c] += y[c];
                         }
+                        #pragma unroll
+                        for (int c = 0; c < 16; c++)
+                            if (m0 + c0 + c < M) ik_st(Y, (size_t)(m0 + c0 + c) * ldy + feature, v[c]);
                     }
                 }
             }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(acc_empty + buf);               // 128 arrivals: this accumulator may be overwritten
         }
     }
+    #undef IK_TILE_COORDS
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
@@ -246,6 +293,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 template <typename TY>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TY* __restrict__ Y, int M, int N, int ldy,
                                      int splits, int accumulate) {
+    ik_pdl_launch_dependents();
+    ik_pdl_wait();
     const size_t total = (size_t)M * N;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         float s = 0.f;
@@ -296,15 +345,17 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial
     if (e != cudaSuccess) return (int)e;
     const int nkb = (K + BK - 1) / BK;
     const int per = (nkb + splits - 1) / splits;
-    dim3 grid((N + BM - 1) / BM, (M + BN - 1) / BN, (nkb + per - 1) / per);
-    kern<<<grid, THREADS, C::SMEM, stream>>>(mw, mx, (TY*)Y, grid.z > 1 ? partial : nullptr, M, N, K, ldy, accumulate,
-                                             per, status);
+    const int n_splits = (nkb + per - 1) / per;
+    const long long total = (long long)((N + BM - 1) / BM) * ((M + BN - 1) / BN) * n_splits;
+    const int blocks = (int)(total < 148 ? total : 148);
+    IK_RETURN_IF_ERROR(ik_launch(kern, blocks, THREADS, C::SMEM, stream, mw, mx, (TY*)Y, n_splits > 1 ? partial : nullptr, M,
+                                 N, K, ldy, accumulate, per, n_splits, status));
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    if (grid.z > 1) {
-        const size_t total = (size_t)M * N;
-        const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-        splitk_reduce_kernel<TY><<<blocks, 256, 0, stream>>>(partial, (TY*)Y, M, N, ldy, (int)grid.z, accumulate);
+    if (n_splits > 1) {
+        const size_t elems = (size_t)M * N;
+        const int rblocks = (int)((elems + 255) / 256 < 148 * 8 ? (elems + 255) / 256 : 148 * 8);
+        IK_RETURN_IF_ERROR(ik_launch(splitk_reduce_kernel<TY>, rblocks, 256, 0, stream, partial, (TY*)Y, M, N, ldy, n_splits, accumulate));
         e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
     }

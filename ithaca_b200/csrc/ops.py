@@ -220,7 +220,6 @@ def gemm_bf16_mma(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] 
 
 N_SM = 148
 
-
 def tcgen05_splits(M: int, N: int, K: int) -> int:
     """K slices for the tcgen05 product: as many as fill the SMs when the output has few tiles.
     Each slice keeps at least four 64-wide K steps."""

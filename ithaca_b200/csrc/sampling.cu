@@ -82,6 +82,8 @@ __device__ Best block_argmax(const float* w, int V, Best* sh /* [32] */) {
 
 __global__ void __launch_bounds__(ST)
 argmax_kernel(const float* __restrict__ logits, int ldl, int* __restrict__ out, int V) {
+    ik_pdl_launch_dependents();
+    ik_pdl_wait();
     __shared__ Best sh[32];
     const Best b = block_argmax(logits + (size_t)blockIdx.x * ldl, V, sh);
     if (threadIdx.x == 0) out[blockIdx.x] = b.i;
@@ -97,6 +99,8 @@ __global__ void __launch_bounds__(ST)
 sample_kernel(const float* __restrict__ logits, int ldl, float* __restrict__ work, int* __restrict__ out, int V,
               float temperature, int top_k, float top_p, float rep_pen, const int* __restrict__ recent, int n_recent,
               uint64_t seed, const int* __restrict__ streams, const int* __restrict__ counters) {
+    ik_pdl_launch_dependents();
+    ik_pdl_wait();
     __shared__ Best shb[32];
     __shared__ float shf[32];
     __shared__ int shi[32];
@@ -224,7 +228,7 @@ sample_kernel(const float* __restrict__ logits, int ldl, float* __restrict__ wor
 IK_EXPORT int ik_argmax(const float* logits, int ldl, int* out, int rows, int V, cudaStream_t stream) {
     if (rows < 0 || V <= 0 || ldl < V) return IK_BAD_ARGUMENT;
     if (rows == 0) return IK_OK;
-    argmax_kernel<<<rows, ST, 0, stream>>>(logits, ldl, out, V);
+    IK_RETURN_IF_ERROR(ik_launch(argmax_kernel, rows, ST, 0, stream, logits, ldl, out, V));
     IK_LAUNCH_STATUS();
 }
 
@@ -234,8 +238,8 @@ IK_EXPORT int ik_sample(const float* logits, int ldl, float* work, int* out, int
                         unsigned long long seed, const int* streams, const int* counters, cudaStream_t stream) {
     if (rows < 0 || V <= 0 || ldl < V || n_recent < 0 || !(rep_pen > 0.f) || !(top_p > 0.f)) return IK_BAD_ARGUMENT;
     if (rows == 0) return IK_OK;
-    sample_kernel<<<rows, ST, 0, stream>>>(logits, ldl, work, out, V, temperature, top_k, top_p, rep_pen, recent,
-                                           n_recent, (uint64_t)seed, streams, counters);
+    IK_RETURN_IF_ERROR(ik_launch(sample_kernel, rows, ST, 0, stream, logits, ldl, work, out, V, temperature, top_k, top_p, rep_pen, recent,
+                                           n_recent, (uint64_t)seed, streams, counters));
     IK_LAUNCH_STATUS();
 }
 
@@ -290,7 +294,7 @@ IK_EXPORT int ik_sample_static(const float* logits, int ldl, int* out, int rows,
     const int st = static_work_address(&work);
     if (st != IK_OK) return st;
     // sample_kernel copies each row's logits into `work` before it reads it: stale contents never show
-    sample_kernel<<<rows, ST, 0, stream>>>(logits, ldl, work, out, V, temperature, top_k, top_p, rep_pen, recent,
-                                           n_recent, (uint64_t)seed, streams, counters);
+    IK_RETURN_IF_ERROR(ik_launch(sample_kernel, rows, ST, 0, stream, logits, ldl, work, out, V, temperature, top_k, top_p, rep_pen, recent,
+                                           n_recent, (uint64_t)seed, streams, counters));
     IK_LAUNCH_STATUS();
 }
