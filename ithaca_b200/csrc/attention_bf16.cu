@@ -459,16 +459,17 @@ IK_EXPORT int ik_attn_prefill(const void* q, const void* k_pages, const void* v_
 IK_EXPORT int ik_attn_decode(const void* q, const void* k_pages, const void* v_pages, void* out, float* part_o,
                              float* part_ml, const int* kv_lens, const int* table, int table_stride, int B, int nh,
                              int nkv, float scale, int window, int page_size, int n_pages, int chunk_pages,
-                             int n_splits, int* status, cudaStream_t stream) {
+                             int n_splits, int ring_kb, int* status, cudaStream_t stream) {
     if (B <= 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size != PAGE || chunk_pages <= 0 || n_splits <= 0 ||
         n_splits > 65535)
         return IK_BAD_ARGUMENT;
     const int G = nh / nkv, n_hc = (G + 15) / 16;
     if ((long long)nkv * n_hc > 65535) return IK_BAD_ARGUMENT;
     dim3 grid(B, nkv * n_hc, n_splits);
-    // as many ring stages as fit ~105 KB (two blocks per SM), at least 2, at most 4
+    // as many ring stages as fit ring_kb (default 105 KB), at least 2, at most 4
     const size_t q_bytes = (size_t)16 * LD * sizeof(bf16), stage_bytes = (size_t)2 * PAGE * LD * sizeof(bf16);
-    int ns = (int)((105 * 1024 - q_bytes) / stage_bytes);
+    if (ring_kb <= 0) ring_kb = 105;
+    int ns = (int)(((size_t)ring_kb * 1024 - q_bytes) / stage_bytes);
     ns = ns < 2 ? 2 : ns > 4 ? 4 : ns;
     const size_t smem = q_bytes + ns * stage_bytes;
 #define IK_DEC(NS_)                                                                                                  \

@@ -17,7 +17,19 @@ from .ops import KernelError, _check, _ptr, _stream
 _vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 _modules: Dict[int, ctypes.CDLL] = {}
 
-DECODE_CHUNK_PAGES = 4        # a decode block covers 4 pages = 256 keys; chunks start at multiples of that
+DECODE_CHUNK_PAGES = 4        # default: a decode block covers 4 pages = 256 keys; chunks start at multiples of that
+
+
+def decode_chunk_pages(n_seqs: int, n_heads: int, n_kv_heads: int, max_kv_len: int, page_size: int = 64) -> int:
+    """Pages per decode block: long chunks (less set-up and merging per byte read) as long as the grid
+    still has at least 128 blocks; 16 pages at most, 2 at least.  Measured on B200 at context 4096:
+    batch 1 -> 4 pages, batch 8 and 64 -> 16 pages."""
+    groups = n_seqs * n_kv_heads * -(-(n_heads // n_kv_heads) // 16)
+    pages = max(1, -(-max_kv_len // page_size))
+    chunk = 16
+    while chunk > 2 and groups * -(-pages // chunk) < 128:
+        chunk //= 2
+    return chunk
 
 
 def supported(head_dim: int) -> bool:
@@ -31,7 +43,7 @@ def module(head_dim: int) -> ctypes.CDLL:
         m = build.load_library(f"ithaca_attn_hd{head_dim}", ["attention_bf16.cu"], defines=[f"IK_HD={head_dim}"])
         m.ik_attn_prefill.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp]
         m.ik_attn_prefill.restype = _i
-        m.ik_attn_decode.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _i, _i, _i,
+        m.ik_attn_decode.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _i, _i, _i, _i,
                                      _vp, _vp]
         m.ik_attn_decode.restype = _i
         if m.ik_attn_head_dim() != head_dim:
@@ -55,7 +67,7 @@ def prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, cu_se
 
 def decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, kv_lens: torch.Tensor, table: torch.Tensor,
            n_seqs: int, kv_len_bound: int, n_heads: int, scale: float, window: int, status: Optional[torch.Tensor],
-           out: Optional[torch.Tensor] = None, chunk_pages: int = DECODE_CHUNK_PAGES) -> torch.Tensor:
+           out: Optional[torch.Tensor] = None, chunk_pages: int = DECODE_CHUNK_PAGES, ring_kb: int = 0) -> torch.Tensor:
     """``kv_len_bound``: no sequence of the step is longer than this (it sizes the grid and the
     scratch for the partial results; blocks beyond a sequence's length return at once)."""
     n_pages, nkv, page_size, hd = k_pages.shape
@@ -67,7 +79,7 @@ def decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, kv_len
         out = torch.empty_like(q)
     _check(m.ik_attn_decode(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(part_o), _ptr(part_ml),
                             _ptr(kv_lens), _ptr(table), table.stride(0), n_seqs, n_heads, nkv, scale, window,
-                            page_size, n_pages, chunk_pages, n_splits, _ptr(status), _stream()), "attention decode", kernels=2)
+                            page_size, n_pages, chunk_pages, n_splits, ring_kb, _ptr(status), _stream()), "attention decode", kernels=2)
     return out
 
 
@@ -79,7 +91,8 @@ def attend(q, k_pages, v_pages, ctx, table, n_heads: int, scale: float, window: 
     if k_pages.dtype != torch.bfloat16 or q.dtype != torch.bfloat16 or page_size != 64 or not supported(hd):
         return None
     if ctx.is_decode:
+        chunk = decode_chunk_pages(ctx.n_seqs, n_heads, nkv, ctx.max_kv_len, page_size)
         return decode(q, k_pages, v_pages, ctx.kv_lens, table, ctx.n_seqs, ctx.kv_len_bound, n_heads, scale, window,
-                      status)
+                      status, chunk_pages=chunk)
     return prefill(q, k_pages, v_pages, ctx.cu_seqlens, ctx.kv_lens, table, ctx.n_seqs, ctx.max_new, n_heads, scale,
                    window, status)

@@ -31,6 +31,12 @@ __device__ __forceinline__ float ik_ld(const __nv_bfloat16* p, size_t i) { retur
 __device__ __forceinline__ void ik_st(float* p, size_t i, float v) { p[i] = v; }
 __device__ __forceinline__ void ik_st(__nv_bfloat16* p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
 
+// silu(g) * u with silu(x) = x / (1 + exp(-x)).
+__device__ __forceinline__ float ik_swiglu(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+// The same with the hardware's approximate exp and reciprocal (relative error ~1e-6), for results that are
+// rounded to bfloat16 anyway.
+__device__ __forceinline__ float ik_swiglu_fast(float g, float u) { return g * __frcp_rn(1.0f + __expf(-g)) * u; }
+
 // Value a float would have after a round trip through the storage type.
 template <typename T> __device__ __forceinline__ float ik_round_to(float v);
 template <> __device__ __forceinline__ float ik_round_to<float>(float v) { return v; }

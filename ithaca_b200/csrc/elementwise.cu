@@ -67,28 +67,30 @@ IK_EXPORT int ik_rmsnorm(const float* x, const int* rows_in, const float* w, voi
 }
 
 // ------------------------------------------------------------------ SwiGLU
-// in: [T, 2*ff] float, gate in columns [0, ff), up in [ff, 2ff).  out[t, j] = silu(g) * u.
+// in: [T, 2*ff] float; gate in columns [0, ff) and up in [ff, 2ff), or, interleaved, gate j in column
+// 2j and up j in column 2j + 1.  out[t, j] = silu(g) * u.
 template <typename TO>
-__global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out, int ff, size_t total) {
+__global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out, int ff, size_t total, int interleaved) {
     ik_pdl_launch_dependents();
     ik_pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / ff;
         const int j = (int)(idx - t * ff);
-        const float g = gu[t * 2 * ff + j], u = gu[t * 2 * ff + ff + j];
-        ik_st(out, idx, g / (1.0f + expf(-g)) * u);
+        const float g = interleaved ? gu[t * 2 * ff + 2 * j] : gu[t * 2 * ff + j];
+        const float u = interleaved ? gu[t * 2 * ff + 2 * j + 1] : gu[t * 2 * ff + ff + j];
+        ik_st(out, idx, ik_swiglu(g, u));
     }
 }
 
-IK_EXPORT int ik_swiglu(const float* gate_up, void* out, int out_dtype, int T, int ff, cudaStream_t stream) {
+IK_EXPORT int ik_swiglu(const float* gate_up, void* out, int out_dtype, int T, int ff, int interleaved, cudaStream_t stream) {
     if (T < 0 || ff <= 0) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
     const size_t total = (size_t)T * ff;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     if (out_dtype == IK_F32)
-        IK_RETURN_IF_ERROR(ik_launch(swiglu_kernel<float>, blocks, 256, 0, stream, gate_up, (float*)out, ff, total));
+        IK_RETURN_IF_ERROR(ik_launch(swiglu_kernel<float>, blocks, 256, 0, stream, gate_up, (float*)out, ff, total, interleaved));
     else if (out_dtype == IK_BF16)
-        IK_RETURN_IF_ERROR(ik_launch(swiglu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, gate_up, (__nv_bfloat16*)out, ff, total));
+        IK_RETURN_IF_ERROR(ik_launch(swiglu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, gate_up, (__nv_bfloat16*)out, ff, total, interleaved));
     else
         return IK_BAD_ARGUMENT;
     IK_LAUNCH_STATUS();
@@ -96,7 +98,7 @@ IK_EXPORT int ik_swiglu(const float* gate_up, void* out, int out_dtype, int T, i
 
 // ------------------------------------------------------------------ rotary + cache append
 // qkv: [T, (nh + 2 nkv) * hd] float, q heads first, then k heads, then v heads.
-// One block per (token, head).  q heads are rotated and stored to q_out [T, nh*hd];
+// One block per (token, group of heads): the token's cos/sin are computed once per block.  q heads are rotated and stored to q_out [T, nh*hd];
 // k heads are rotated and stored into the token's place in the key pages; v heads are
 // stored into the value pages.  A page holds page_size positions of every kv head:
 // pages[page][kv_head][position in page][hd].  The page of position p of sequence s is
@@ -106,47 +108,70 @@ IK_EXPORT int ik_swiglu(const float* gate_up, void* out, int out_dtype, int T, i
 // functions.  pairing 0 rotates (i, i + rot/2), pairing 1 rotates (2i, 2i + 1); dimensions
 // from rot upward pass through.
 template <typename TQ, typename TC>
-__global__ void rope_append_kernel(const float* __restrict__ qkv, TQ* __restrict__ q_out, TC* __restrict__ k_pages,
-                                   TC* __restrict__ v_pages, const int* __restrict__ token_seq,
-                                   const int* __restrict__ token_pos, const int* __restrict__ table, int table_stride,
-                                   const float* __restrict__ inv_freq, int nh, int nkv, int hd, int rot, int pairing,
-                                   int page_size, int n_pages, int write_cache, int* status) {
+__global__ void __launch_bounds__(256)
+rope_append_kernel(const float* __restrict__ qkv, TQ* __restrict__ q_out, TC* __restrict__ k_pages,
+                   TC* __restrict__ v_pages, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
+                   const int* __restrict__ table, int table_stride, const float* __restrict__ inv_freq, int nh, int nkv,
+                   int hd, int rot, int pairing, int page_size, int n_pages, int write_cache, int heads_per_block,
+                   int* status) {
+    extern __shared__ float cs[];                  // [rot/2] cos, then [rot/2] sin of this token's angles
     ik_pdl_launch_dependents();
     ik_pdl_wait();
-    const int t = blockIdx.x, head = blockIdx.y;
+    const int t = blockIdx.x, half = rot / 2;
+    const int head_lo = blockIdx.y * heads_per_block;                          // over q heads, then k heads, then v heads
+    const int head_hi = min(head_lo + heads_per_block, nh + 2 * nkv);
     const int pos = token_pos[t];
-    const float* src = qkv + (size_t)t * (nh + 2 * nkv) * hd + (size_t)head * hd;
-    const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
-    if (!is_q && !write_cache) return;
-    size_t dst_off = 0;
-    if (!is_q) {
-        const int seq = token_seq[t];
-        const int page = table[(size_t)seq * table_stride + pos / page_size];
-        if (page < 0 || page >= n_pages) {          // never write outside the pool
-            if (threadIdx.x == 0 && status) atomicExch(status, 2);
-            return;
-        }
-        const int kvh = is_k ? head - nh : head - nh - nkv;
-        dst_off = (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * hd;
-    }
-    if (is_q || is_k) {
-        const int half = rot / 2;
+    if (head_lo < nh + nkv) {
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
-            const int i0 = pairing == 0 ? i : 2 * i, i1 = pairing == 0 ? i + half : 2 * i + 1;
             const float ang = __fmul_rn((float)pos, inv_freq[i]);
-            const float c = cosf(ang), s = sinf(ang);
-            const float a = src[i0], b = src[i1];
-            const float r0 = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
-            const float r1 = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
-            if (is_q) { ik_st(q_out, (size_t)t * nh * hd + (size_t)head * hd + i0, r0); ik_st(q_out, (size_t)t * nh * hd + (size_t)head * hd + i1, r1); }
-            else { ik_st(k_pages, dst_off + i0, r0); ik_st(k_pages, dst_off + i1, r1); }
+            cs[i] = cosf(ang);
+            cs[half + i] = sinf(ang);
         }
-        for (int i = rot + threadIdx.x; i < hd; i += blockDim.x) {
-            if (is_q) ik_st(q_out, (size_t)t * nh * hd + (size_t)head * hd + i, src[i]);
-            else ik_st(k_pages, dst_off + i, src[i]);
+    }
+    // where this token's keys and values go
+    size_t page_off = 0;
+    bool page_ok = false;
+    if (write_cache && head_hi > nh) {
+        const int page = table[(size_t)token_seq[t] * table_stride + pos / page_size];
+        page_ok = page >= 0 && page < n_pages;
+        if (!page_ok) { if (threadIdx.x == 0 && status) atomicExch(status, 2); }       // never write outside the pool
+        else page_off = ((size_t)page * nkv * page_size + (pos % page_size)) * hd;
+    }
+    __syncthreads();
+    const float* src = qkv + (size_t)t * (nh + 2 * nkv) * hd;
+    const int n_heads = head_hi - head_lo;
+    // rotated pairs of the q and k heads of this block
+    for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
+        const int head = head_lo + idx / half, i = idx % half;
+        if (head >= nh + nkv) break;                                           // v heads follow; handled below
+        const bool is_q = head < nh;
+        if (!is_q && !page_ok) continue;
+        const int i0 = pairing == 0 ? i : 2 * i, i1 = pairing == 0 ? i + half : 2 * i + 1;
+        const float c = cs[i], sn = cs[half + i];
+        const float a = src[(size_t)head * hd + i0], b = src[(size_t)head * hd + i1];
+        const float r0 = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn));
+        const float r1 = __fadd_rn(__fmul_rn(a, sn), __fmul_rn(b, c));
+        if (is_q) {
+            const size_t o = ((size_t)t * nh + head) * hd;
+            ik_st(q_out, o + i0, r0);
+            ik_st(q_out, o + i1, r1);
+        } else {
+            const size_t o = page_off + (size_t)(head - nh) * page_size * hd;
+            ik_st(k_pages, o + i0, r0);
+            ik_st(k_pages, o + i1, r1);
         }
-    } else {
-        for (int i = threadIdx.x; i < hd; i += blockDim.x) ik_st(v_pages, dst_off + i, src[i]);
+    }
+    // dimensions beyond the rotated width pass through; value heads are copied whole
+    for (int idx = threadIdx.x; idx < n_heads * hd; idx += blockDim.x) {
+        const int head = head_lo + idx / hd, i = idx % hd;
+        if (head < nh + nkv) {
+            if (i < rot) continue;
+            const float v = src[(size_t)head * hd + i];
+            if (head < nh) ik_st(q_out, ((size_t)t * nh + head) * hd + i, v);
+            else if (page_ok) ik_st(k_pages, page_off + (size_t)(head - nh) * page_size * hd + i, v);
+        } else if (page_ok) {
+            ik_st(v_pages, page_off + (size_t)(head - nh - nkv) * page_size * hd + i, src[(size_t)head * hd + i]);
+        }
     }
 }
 
@@ -157,11 +182,14 @@ IK_EXPORT int ik_rope_append(const float* qkv, void* q_out, int q_dtype, void* k
     if (T < 0 || nh <= 0 || nkv <= 0 || hd <= 0 || rot < 0 || rot > hd || (rot & 1) || page_size <= 0) return IK_BAD_ARGUMENT;
     if (rot > 0 && !inv_freq) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
-    dim3 grid(T, nh + 2 * nkv);
-    const int threads = 64;
+    // few tokens (decode): spread a token's heads over several blocks; many tokens: one block per token
+    const int hpb = T >= 256 ? nh + 2 * nkv : 4;
+    dim3 grid(T, (nh + 2 * nkv + hpb - 1) / hpb);
+    const int threads = 256;
+    const size_t smem = (size_t)rot * sizeof(float);
 #define IK_ROPE(TQ, TC)                                                                                             \
-    IK_RETURN_IF_ERROR(ik_launch(rope_append_kernel<TQ, TC>, grid, threads, 0, stream, qkv, (TQ*)q_out, (TC*)k_pages, (TC*)v_pages, token_seq, \
-        token_pos, table, table_stride, inv_freq, nh, nkv, hd, rot, pairing, page_size, n_pages, write_cache, status))
+    IK_RETURN_IF_ERROR(ik_launch(rope_append_kernel<TQ, TC>, grid, threads, smem, stream, qkv, (TQ*)q_out, (TC*)k_pages, (TC*)v_pages, token_seq, \
+        token_pos, table, table_stride, inv_freq, nh, nkv, hd, rot, pairing, page_size, n_pages, write_cache, hpb, status))
     if (q_dtype == IK_F32 && cache_dtype == IK_F32) IK_ROPE(float, float);
     else if (q_dtype == IK_BF16 && cache_dtype == IK_BF16) IK_ROPE(__nv_bfloat16, __nv_bfloat16);
     else if (q_dtype == IK_F32 && cache_dtype == IK_BF16) IK_ROPE(float, __nv_bfloat16);

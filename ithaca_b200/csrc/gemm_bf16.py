@@ -26,3 +26,19 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, a
     if done is None:
         ops.gemm_simt(x, w, out=out, accumulate=accumulate)
     return out
+
+
+def gemm_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """h = silu(x Wg^T) * (x Wu^T) in one kernel.  ``w_interleaved``: [2 ff, d] with gate j in row 2j and
+    up j in row 2j + 1, so that a product tile holds both halves of every pair it covers and the
+    [tokens, 2 ff] intermediate is never written."""
+    M, ff = x.shape[0], w_interleaved.shape[0] // 2
+    out = torch.empty((M, ff), dtype=out_dtype, device=x.device)
+    if M <= SKINNY_MAX_TOKENS:
+        done = ops.gemm_bf16_mma(x, w_interleaved, out=out, kind=1, swiglu=True)
+    else:
+        done = ops.gemm_tcgen05(x, w_interleaved, out=out, status=ops.device_status(x.device), swiglu=True)
+    if done is None:
+        gu = ops.gemm_simt(x, w_interleaved, out_dtype=torch.float32)
+        ops.swiglu(gu, out_dtype, out=out, interleaved=True)
+    return out

@@ -144,7 +144,7 @@ template <int BN, typename TY>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     TY* __restrict__ Y, float* __restrict__ partial, int M, int N, int K, int ldy, int accumulate,
-                    int kb_per_split, int n_splits, int* status) {
+                    int swiglu, int kb_per_split, int n_splits, int* status) {
     typedef Cfg<BN> C;
     extern __shared__ unsigned char smem_raw[];
     ik_pdl_launch_dependents();
@@ -256,11 +256,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 if (m0 + c0 >= M) break;
                 float v[16];
                 tmem_ld16(acc + c0, v);
-                if (feature < N) {
+                if (feature < N || (swiglu && !partial)) {     // N is even under swiglu: a pair is in or out together
                     if (partial) {
                         #pragma unroll
                         for (int c = 0; c < 16; c++)
                             if (m0 + c0 + c < M) partial[((size_t)z * M + m0 + c0 + c) * N + feature] = v[c];
+                    } else if (swiglu) {
+                        // lanes (2j, 2j + 1) hold gate j and up j.  The pair shares the work: the even lane takes
+                        // columns 0..7 (it gets the up values from its neighbour), the odd lane columns 8..15.
+                        const bool odd = lane & 1;
+                        #pragma unroll
+                        for (int c = 0; c < 8; c++) {
+                            const float other = __shfl_xor_sync(0xffffffffu, odd ? v[c] : v[c + 8], 1);
+                            const float gte = odd ? other : v[c], up = odd ? v[c + 8] : other;
+                            const int m = m0 + c0 + c + (odd ? 8 : 0);
+                            if (feature < N && m < M) ik_st(Y, (size_t)m * ldy + (feature >> 1), ik_swiglu_fast(gte, up));
+                        }
                     } else {
                         if (accumulate) {
                             float y[16];
@@ -292,10 +303,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // Adds the K slices in slice order and writes Y.
 template <typename TY>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TY* __restrict__ Y, int M, int N, int ldy,
-                                     int splits, int accumulate) {
+                                     int splits, int accumulate, int swiglu) {
     ik_pdl_launch_dependents();
     ik_pdl_wait();
     const size_t total = (size_t)M * N;
+    if (swiglu) {                       // columns (2j, 2j + 1) are gate j and up j; Y is [M, N / 2]
+        const size_t half = (size_t)M * (N / 2);
+        for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < half; idx += (size_t)gridDim.x * blockDim.x) {
+            const size_t m = idx / (N / 2), j = idx - m * (N / 2);
+            float g = 0.f, u = 0.f;
+            for (int z = 0; z < splits; z++) {
+                g += partial[(size_t)z * total + m * N + 2 * j];
+                u += partial[(size_t)z * total + m * N + 2 * j + 1];
+            }
+            ik_st(Y, m * ldy + j, ik_swiglu(g, u));
+        }
+        return;
+    }
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         float s = 0.f;
         for (int z = 0; z < splits; z++) s += partial[(size_t)z * total + idx];
@@ -338,7 +362,7 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int bo
 
 template <int BN, typename TY>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial, int M, int N, int K, int ldy,
-           int accumulate, int splits, int* status, cudaStream_t stream) {
+           int accumulate, int swiglu, int splits, int* status, cudaStream_t stream) {
     typedef Cfg<BN> C;
     auto kern = gemm_tcgen05_kernel<BN, TY>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
@@ -349,13 +373,13 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial
     const long long total = (long long)((N + BM - 1) / BM) * ((M + BN - 1) / BN) * n_splits;
     const int blocks = (int)(total < 148 ? total : 148);
     IK_RETURN_IF_ERROR(ik_launch(kern, blocks, THREADS, C::SMEM, stream, mw, mx, (TY*)Y, n_splits > 1 ? partial : nullptr, M,
-                                 N, K, ldy, accumulate, per, n_splits, status));
+                                 N, K, ldy, accumulate, swiglu, per, n_splits, status));
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (n_splits > 1) {
         const size_t elems = (size_t)M * N;
         const int rblocks = (int)((elems + 255) / 256 < 148 * 8 ? (elems + 255) / 256 : 148 * 8);
-        IK_RETURN_IF_ERROR(ik_launch(splitk_reduce_kernel<TY>, rblocks, 256, 0, stream, partial, (TY*)Y, M, N, ldy, n_splits, accumulate));
+        IK_RETURN_IF_ERROR(ik_launch(splitk_reduce_kernel<TY>, rblocks, 256, 0, stream, partial, (TY*)Y, M, N, ldy, n_splits, accumulate, swiglu));
         e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
     }
@@ -369,9 +393,12 @@ IK_EXPORT int ik_gemm_tcgen05_tile(int M) { return M <= 32 ? 32 : M <= 64 ? 64 :
 
 // splits > 1 needs `partial`: splits * M * N floats of scratch owned by the caller.
 // status: device int; set to 4 if a block gave up waiting (the result is then not to be used).
+// swiglu: W holds (gate j, up j) in rows (2j, 2j + 1); Y is [M, N / 2] = silu(gate) * up.
 IK_EXPORT int ik_gemm_tcgen05(const void* X, const void* W, void* Y, int y_dtype, float* partial, int M, int N, int K,
-                              int ldx, int ldw, int ldy, int accumulate, int splits, int* status, cudaStream_t stream) {
-    if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || ldy < N || splits < 1) return IK_BAD_ARGUMENT;
+                              int ldx, int ldw, int ldy, int accumulate, int swiglu, int splits, int* status,
+                              cudaStream_t stream) {
+    if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || ldy < (swiglu ? N / 2 : N) || splits < 1) return IK_BAD_ARGUMENT;
+    if (swiglu && ((N & 1) || accumulate)) return IK_BAD_ARGUMENT;
     if (y_dtype != IK_F32 && y_dtype != IK_BF16) return IK_BAD_ARGUMENT;
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return IK_UNSUPPORTED;
     if (splits > 1 && !partial) return IK_BAD_ARGUMENT;
@@ -383,8 +410,8 @@ IK_EXPORT int ik_gemm_tcgen05(const void* X, const void* W, void* Y, int y_dtype
     st = make_map(&mx, X, M, K, ldx, bn);
     if (st != IK_OK) return st;
 #define IK_TC(BN_)                                                                                                       \
-    return y_dtype == IK_F32 ? launch<BN_, float>(mw, mx, Y, partial, M, N, K, ldy, accumulate, splits, status, stream)    \
-                             : launch<BN_, bf16>(mw, mx, Y, partial, M, N, K, ldy, accumulate, splits, status, stream)
+    return y_dtype == IK_F32 ? launch<BN_, float>(mw, mx, Y, partial, M, N, K, ldy, accumulate, swiglu, splits, status, stream) \
+                             : launch<BN_, bf16>(mw, mx, Y, partial, M, N, K, ldy, accumulate, swiglu, splits, status, stream)
     switch (bn) {
         case 32: IK_TC(32);
         case 64: IK_TC(64);

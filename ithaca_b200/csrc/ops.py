@@ -69,11 +69,11 @@ def _check(status: int, what: str, kernels: int = 1) -> None:
 _SIGNATURES = {
     "ik_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _f, _vp, _vp],
     "ik_rmsnorm": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
-    "ik_swiglu": [_vp, _vp, _i, _i, _i, _vp],
+    "ik_swiglu": [_vp, _vp, _i, _i, _i, _i, _vp],
     "ik_rope_append": [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "ik_gemm_bf16_mma": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "ik_gemm_tcgen05": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "ik_gemm_bf16_mma": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "ik_gemm_tcgen05": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_gemm_tcgen05_tile": [_i],
     "ik_attention_simt": [_vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp],
     "ik_argmax": [_vp, _i, _vp, _i, _i, _vp],
@@ -138,14 +138,16 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def swiglu(gate_up: torch.Tensor, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None,
+           interleaved: bool = False) -> torch.Tensor:
+    """``interleaved``: gate j and up j sit in columns 2j and 2j + 1 instead of j and ff + j."""
     _need(gate_up, "gate_up", torch.float32)
     T, ff2 = gate_up.shape
     if ff2 % 2:
         raise KernelError("swiglu: the input needs an even number of columns (gate then up)")
     if out is None:
         out = torch.empty((T, ff2 // 2), dtype=out_dtype, device=gate_up.device)
-    _check(lib().ik_swiglu(_ptr(gate_up), _ptr(out), _code(out), T, ff2 // 2, _stream()), "swiglu")
+    _check(lib().ik_swiglu(_ptr(gate_up), _ptr(out), _code(out), T, ff2 // 2, 1 if interleaved else 0, _stream()), "swiglu")
     return out
 
 
@@ -193,7 +195,7 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
 
 
 def gemm_bf16_mma(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=torch.float32,
-                  accumulate: bool = False, kind: int = 0) -> Optional[torch.Tensor]:
+                  accumulate: bool = False, kind: int = 0, swiglu: bool = False) -> Optional[torch.Tensor]:
     """bfloat16 operands, float accumulation on the warp-level tensor-core path.  ``kind``: 0 = by
     M, 1 = the skinny (decode) kernel, 2 = the tiled kernel.  Returns None when the kernels
     do not take these sizes (K not a multiple of 8, unaligned rows)."""
@@ -203,15 +205,16 @@ def gemm_bf16_mma(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] 
     N, K2 = w.shape
     if K != K2 or x.stride(1) != 1 or w.stride(1) != 1:
         raise KernelError(f"gemm: shapes {tuple(x.shape)} x {tuple(w.shape)}^T do not match or rows are not contiguous")
+    n_out = N // 2 if swiglu else N
     if out is None:
         if accumulate:
             raise KernelError("gemm: accumulate needs an output to add to")
-        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     _need(out, "out", contiguous=False)
-    if out.shape != (M, N) or out.stride(1) != 1:
+    if out.shape != (M, n_out) or out.stride(1) != 1:
         raise KernelError("gemm: the output has the wrong shape")
     st = lib().ik_gemm_bf16_mma(_ptr(x), _ptr(w), _ptr(out), _code(out), M, N, K, x.stride(0), w.stride(0),
-                                out.stride(0), 1 if accumulate else 0, kind, _stream())
+                                out.stride(0), 1 if accumulate else 0, kind, 1 if swiglu else 0, _stream())
     if st == -2:
         return None
     _check(st, "gemm_bf16_mma")
@@ -231,7 +234,7 @@ def tcgen05_splits(M: int, N: int, K: int) -> int:
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=torch.float32,
                  accumulate: bool = False, splits: Optional[int] = None,
-                 status: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+                 status: Optional[torch.Tensor] = None, swiglu: bool = False) -> Optional[torch.Tensor]:
     """bfloat16 operands on the tcgen05 tensor cores (TMA-fed, accumulators in TMEM).  Returns None
     when the kernel does not take these sizes (K not a multiple of 8, unaligned rows)."""
     _need(x, "x", torch.bfloat16, contiguous=False)
@@ -242,18 +245,20 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
         raise KernelError(f"gemm: shapes {tuple(x.shape)} x {tuple(w.shape)}^T do not match or rows are not contiguous")
     if K % 8 or x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16:
         return None
+    n_out = N // 2 if swiglu else N
     if out is None:
         if accumulate:
             raise KernelError("gemm: accumulate needs an output to add to")
-        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     _need(out, "out", contiguous=False)
-    if out.shape != (M, N) or out.stride(1) != 1:
+    if out.shape != (M, n_out) or out.stride(1) != 1:
         raise KernelError("gemm: the output has the wrong shape")
     if splits is None:
         splits = tcgen05_splits(M, N, K)
     partial = torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None
     st = lib().ik_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(out), _code(out), _ptr(partial), M, N, K, x.stride(0),
-                               w.stride(0), out.stride(0), 1 if accumulate else 0, splits, _ptr(status), _stream())
+                               w.stride(0), out.stride(0), 1 if accumulate else 0, 1 if swiglu else 0, splits, _ptr(status),
+                               _stream())
     if st == -2:
         return None
     _check(st, "gemm_tcgen05", kernels=2 if splits > 1 else 1)

@@ -34,10 +34,21 @@ class GatedMLP:
         self.gate_up = Linear([tensors[w["gate"]], tensors[w["up"]]], runtime)
         self.down = Linear([tensors[w["down"]]], runtime)
         self.runtime = runtime
+        # bfloat16 path: rows interleaved (gate 0, up 0, gate 1, up 1, ...) so that the product's epilogue
+        # can apply silu(gate) * up itself and the [tokens, 2 ff] intermediate never exists
+        self.fused = runtime.dtype == "bfloat16"
+        if self.fused:
+            ff, d = self.intermediate, self.hidden
+            wgu = self.gate_up.weight
+            self.gate_up.weight = torch.stack((wgu[:ff], wgu[ff:]), dim=1).reshape(2 * ff, d).contiguous()
 
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
-        gu = self.gate_up(x, out_dtype=torch.float32)
-        h = ops.swiglu(gu, self.runtime.act_dtype)
+        if self.fused:
+            from ..csrc import gemm_bf16
+            h = gemm_bf16.gemm_swiglu(x, self.gate_up.weight, self.runtime.act_dtype)
+        else:
+            gu = self.gate_up(x, out_dtype=torch.float32)
+            h = ops.swiglu(gu, self.runtime.act_dtype)
         self.down(h, out=residual, accumulate=True)
 
 

@@ -141,6 +141,35 @@ def test_gemm_tcgen05_strided_rows_and_default_splits():
     assert ops().gemm_tcgen05(xb[:, 4:516], wb[:, :512], status=status) is None          # rows not 16-byte aligned
 
 
+@pytest.mark.parametrize("M", [1, 8, 13, 16, 17, 64, 300])
+@pytest.mark.parametrize("ff,d", [(172, 64), (512, 192), (1000, 264), (4096, 1024)])
+def test_gate_up_product_with_swiglu_epilogue(M, ff, d):
+    """h = silu(x Wg^T) * (x Wu^T) from one kernel over row-interleaved weights, every dispatch path."""
+    from ithaca_b200.csrc import gemm_bf16
+    x = rnd((M, d), 21, torch.bfloat16)
+    wg, wu = rnd((ff, d), 22, torch.bfloat16, 0.3), rnd((ff, d), 23, torch.bfloat16, 0.3)
+    ref = P.silu(x.double() @ wg.double().T) * (x.double() @ wu.double().T)
+    wi = torch.stack((wg, wu), dim=1).reshape(2 * ff, d).contiguous().to(DEV)
+    got = gemm_bf16.gemm_swiglu(x.to(DEV), wi)
+    assert got.dtype == torch.bfloat16 and got.shape == (M, ff)
+    close(got, ref, 6e-3)
+    status = ops().device_status(DEV)
+    if M > 16:
+        for splits in (1, 3):
+            got = ops().gemm_tcgen05(x.to(DEV), wi, out_dtype=torch.float32, splits=min(splits, -(-d // 64)), status=status,
+                                     swiglu=True)
+            close(got, ref, 2e-5)
+    else:
+        close(ops().gemm_bf16_mma(x.to(DEV), wi, out_dtype=torch.float32, kind=1, swiglu=True), ref, 2e-5)
+    assert status.item() == 0
+
+
+def test_swiglu_kernel_interleaved():
+    gu = rnd((5, 2 * 172), 24, scale=2.0)
+    ref = P.silu(gu[:, 0::2].double()) * gu[:, 1::2].double()
+    close(ops().swiglu(gu.to(DEV), torch.float32, interleaved=True), ref, 2e-6)
+
+
 def test_gemm_bf16_refuses_unaligned_k():
     x, w = rnd((4, 172), 14, torch.bfloat16), rnd((64, 172), 15, torch.bfloat16)
     assert ops().gemm_bf16_mma(x.to(DEV), w.to(DEV)) is None           # K % 8 != 0
@@ -280,8 +309,9 @@ def test_attention_bf16_decode(nh, nkv, hd, window):
     c = attention_case(nh, nkv, hd, lens, new, window or None, torch.bfloat16, seed=32)
     k_d, v_d, tab = c["pg"].dev()
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    for bound in (max(lens), 2048):                                     # a larger grid must not change anything
-        got = A.decode(c["q"], k_d, v_d, c["kv_lens"], tab, len(lens), bound, nh, 1 / math.sqrt(hd), window, status)
+    for bound, chunk in ((max(lens), 4), (2048, 4), (max(lens), 2), (2048, 16)):   # a larger grid or other chunks change nothing
+        got = A.decode(c["q"], k_d, v_d, c["kv_lens"], tab, len(lens), bound, nh, 1 / math.sqrt(hd), window, status,
+                       chunk_pages=chunk)
         assert status.item() == 0
         close(got, c["ref"], 8e-3)
 
