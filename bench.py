@@ -144,7 +144,7 @@ def e2e_run(eng, batch, steps, vocab, context):
     st = eng.last_stats
     assert all(len(o) == steps + 1 for o in out)
     # the first token of each sequence comes from the prefill step; the decode clock covers the rest
-    return {"tok_s": batch * steps / st.decode_seconds, "h2d": eng.stepper.builder.last_upload_bytes, "d2h": batch * 4 + 4}
+    return {"tok_s": batch * steps / st.decode_seconds, "h2d": eng._decoder.last_upload_bytes, "d2h": batch * 4 + 4}
 
 
 def prefill_run(eng, tokens, vocab, reps=3):

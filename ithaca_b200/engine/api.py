@@ -96,11 +96,9 @@ class Engine:
 
     def step_and_sample(self, slots, tokens, streams, counters, recent) -> List[int]:
         if self._decoder is not None and all(len(t) == 1 for t in tokens):
-            ids = self._decoder.step_and_sample(slots, tokens, streams, counters, recent, self._sampler)
-        else:
-            logits = self.stepper.step(slots, tokens, "last")
-            ids = self._sampler.sample(logits, streams, counters, recent)
-        host = ids.cpu()                      # waits for the step
+            return self._decoder.step_and_sample(slots, tokens, streams, counters, recent, self._sampler)
+        logits = self.stepper.step(slots, tokens, "last")
+        host = self._sampler.sample(logits, streams, counters, recent).cpu()      # waits for the step
         self.stepper.check_status()
         return host.tolist()
 

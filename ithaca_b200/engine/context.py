@@ -36,6 +36,16 @@ class StepContext:
     host_kv_lens: List[int] = field(default_factory=list)
 
 
+def field_offsets(sizes):
+    """Where each field of a step's description starts in the packed int32 buffer: every field on a
+    16-byte boundary.  Returns (offsets, sizes, total length)."""
+    offs, total = [], 0
+    for n in sizes:
+        offs.append(total)
+        total += (n + 3) // 4 * 4
+    return offs, list(sizes), max(total, 4)
+
+
 class ContextBuilder:
     """Reusable pinned staging so that a step costs one host-to-device copy."""
 
@@ -70,13 +80,7 @@ class ContextBuilder:
         kv_lens = np.asarray(start, dtype=np.int32) + np.asarray(n_new, dtype=np.int32)
         parts = [token_ids, token_seq, token_pos, cu, np.asarray(slots, dtype=np.int32), kv_lens, rows]
         parts += [np.ascontiguousarray(t, dtype=np.int32).reshape(-1) for t in tables]
-        sizes = [p.size for p in parts]
-        # every field starts on a 16-byte boundary
-        offs, total = [], 0
-        for s in sizes:
-            offs.append(total)
-            total += (s + 3) // 4 * 4
-        total = max(total, 4)
+        offs, sizes, total = field_offsets([p.size for p in parts])
         if self._copied is not None:
             self._copied.synchronize()                        # the staging buffer is free again
         stage = self._staging(total)

@@ -7,27 +7,43 @@ device memory (src/model.cpp:1341-1350, src/cuda_tier.cpp:630-651).  Here a grap
 is captured per (number of sequences, block-table width): the step's description
 (tokens, positions, lengths, block tables) lives in one device buffer that is
 refilled before each replay, so the same graph serves every step of that shape.
-The graph covers the forward pass and, for greedy sampling, the argmax.
+The graph covers the forward pass, the greedy pick, and a copy of the kernels'
+status word next to the picked ids, so that one read-back per step brings both.
+
+The host side of a replayed step is kept short: the description is written
+straight into one of two pinned staging buffers (the other may still be in
+flight), only the fields that change from step to step are rewritten, and the
+cache's bookkeeping for "one more position per sequence" is done with array
+operations.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
+from ..cache.pages import CacheError
 from ..csrc import ops
-from .context import StepContext
-from .step import Stepper
+from .context import StepContext, field_offsets
+from .step import StepError, Stepper
 
 
 @dataclass
 class _Captured:
     graph: torch.cuda.CUDAGraph
-    buffer: torch.Tensor
+    buffer: torch.Tensor                 # device int32: the step's description
+    offsets: List[int]
+    sizes: List[int]
+    stages: List[torch.Tensor]           # two pinned copies of the description
+    stage_events: List[Optional[torch.cuda.Event]]
+    stage_slots: List[Optional[Tuple[int, ...]]]
     logits: torch.Tensor
-    ids: torch.Tensor
+    out: torch.Tensor                    # device int32 [B + 1]: greedy ids, then the status word
+    host_out: torch.Tensor               # pinned copy of ``out``
     launches: int
+    turn: int = 0
 
 
 def _bucket(cols: int) -> int:
@@ -43,64 +59,137 @@ class GraphDecoder:
         self.stepper = stepper
         self.graphs: Dict[Tuple[int, int], _Captured] = {}
         self.launches_last_step = 0
+        self._read_back = torch.cuda.Event()
+        self.last_upload_bytes = 0
 
-    def _table_cols(self, slots: Sequence[int]) -> int:
-        page = self.stepper.cache.page_size
-        need = max(-(-(self.stepper.cache.length(s) + 1) // page) for s in slots)
-        return _bucket(need)
-
+    # -- one decode step -------------------------------------------------------------------------
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]]) -> Tuple[torch.Tensor, torch.Tensor]:
-        """One token per slot.  Returns (logits [B, vocab], argmax ids [B]); both are the
-        graph's own buffers and are overwritten by the next step of the same shape."""
+        """One token per slot.  Returns (logits [B, vocab], greedy ids [B]) on the device; both are
+        the graph's own buffers and are overwritten by the next step of the same shape."""
+        cap = self._run(slots, tokens)
+        return cap.logits, cap.out[:len(slots)]
+
+    def step_to_host(self, slots: Sequence[int], tokens: Sequence[Sequence[int]]) -> Tuple[torch.Tensor, List[int]]:
+        """As ``step``, then waits for the step and returns (logits on the device, greedy ids on the
+        host).  Raises if a kernel reported an index out of range during the step."""
+        cap = self._run(slots, tokens)
+        cap.host_out.copy_(cap.out, non_blocking=True)
+        self._read_back.record()
+        self._read_back.synchronize()
+        got = cap.host_out.tolist()
+        if got[-1] != 0:
+            self.stepper.check_status()
+        return cap.logits, got[:-1]
+
+    def _run(self, slots, tokens) -> _Captured:
         st = self.stepper
+        table = st.cache.table
+        page = st.cache.page_size
         B = len(slots)
-        cols = self._table_cols(slots)
-        key = (B, cols)
-        cap = self.graphs.get(key)
+        if B == 0 or len(tokens) != B:
+            raise StepError("one token per slot is needed")
+        idx = np.asarray(slots, dtype=np.int64)
+        if idx.min() < 0 or idx.max() >= table.max_slots or not table._in_use[idx].all():
+            raise StepError("a slot of this step is not in use")
+        if len(set(slots)) != B:
+            raise StepError("a slot appears twice in one step")
+        toks = np.fromiter((t[0] for t in tokens), dtype=np.int64, count=B)
+        if any(len(t) != 1 for t in tokens):
+            raise StepError("a decode step brings exactly one token per slot")
+        if toks.min() < 0 or toks.max() >= st.vocab_size:
+            raise StepError(f"a token id is outside the vocabulary [0, {st.vocab_size})")
+        lens = table.length[idx]
+        if int(lens.max()) + 1 > st.max_position:
+            raise StepError(f"a sequence would exceed the model's limit of {st.max_position} positions")
+        cols = _bucket(int(-(-(int(lens.max()) + 1) // page)))
+        cap = self.graphs.get((B, cols))
         if cap is None:
             cap = self._capture(slots, tokens, cols)
-            self.graphs[key] = cap
+            self.graphs[(B, cols)] = cap
             self.launches_last_step = cap.launches
-            return cap.logits, cap.ids
-        ctx = st.prepare(slots, tokens, "last", into=cap.buffer, table_cols=cols)
+            return cap
+        # pages: a sequence needs a new one only when it stands at a page boundary
+        for s in idx[table._reserved[idx] <= lens]:
+            table.reserve(int(s), 1)
+        # the description, into the staging buffer that is not in flight
+        cap.turn ^= 1
+        k = cap.turn
+        if cap.stage_events[k] is not None:
+            cap.stage_events[k].synchronize()
+        sn = cap.stages[k].numpy()
+        o = cap.offsets
+        sn[o[0]:o[0] + B] = toks
+        sn[o[2]:o[2] + B] = lens
+        sn[o[5]:o[5] + B] = lens + 1
+        key = tuple(slots)
+        if cap.stage_slots[k] != key:
+            sn[o[1]:o[1] + B] = np.arange(B)
+            sn[o[3]:o[3] + B + 1] = np.arange(B + 1)
+            sn[o[4]:o[4] + B] = idx
+            sn[o[6]:o[6] + B] = np.arange(B)
+            cap.stage_slots[k] = key
+        for g in range(len(st.cache.kv_groups)):
+            t = table.tables[g]
+            dst = sn[o[7 + g]:o[7 + g] + B * cols].reshape(B, cols)
+            c = min(cols, t.shape[1])
+            dst[:, :c] = t[idx, :c]
+            if c < cols:
+                dst[:, c:] = -1
+        cap.buffer.copy_(cap.stages[k], non_blocking=True)
+        if cap.stage_events[k] is None:
+            cap.stage_events[k] = torch.cuda.Event()
+        cap.stage_events[k].record()
+        self.last_upload_bytes = cap.buffer.numel() * 4
         cap.graph.replay()
-        st.finish(ctx)
+        # the sequences are one position longer
+        if any(g.window is not None for g in st.cache.kv_groups):
+            for s in slots:
+                table.commit(int(s), 1)
+        else:
+            table.length[idx] += 1
         self.launches_last_step = cap.launches
-        return cap.logits, cap.ids
+        return cap
 
     def _capture(self, slots, tokens, cols) -> _Captured:
         """The first step of a shape runs eagerly (it also compiles whatever the model still
-        needs) and is then captured; capture does not execute, so the cache is written once."""
+        needs) and is then captured; capture does not execute, so the cache is written once more
+        with the same values when the fresh graph is replayed."""
         st = self.stepper
         page = st.cache.page_size
-        probe = st.prepare(slots, tokens, "last", table_cols=cols)
-        buffer = torch.empty(max(self._buffer_size(probe), 4), dtype=torch.int32, device=st.runtime.device)
+        B = len(slots)
+        n_groups = len(st.cache.kv_groups)
+        offsets, sizes, total = field_offsets([B, B, B, B + 1, B, B, B] + [B * cols] * n_groups)
+        buffer = torch.empty(total, dtype=torch.int32, device=st.runtime.device)
         ctx = st.prepare(slots, tokens, "last", into=buffer, table_cols=cols)
         ctx.kv_len_bound = cols * page
         torch.cuda.current_stream().synchronize()
         st.model.forward(ctx, st.cache)                      # eager warm-up: writes this step's keys and values
         torch.cuda.current_stream().synchronize()
+        out = torch.empty(B + 1, dtype=torch.int32, device=st.runtime.device)
         graph = torch.cuda.CUDAGraph()
         n0 = ops.launch_count()
         with torch.cuda.graph(graph):
             logits = st.model.forward(ctx, st.cache)
-            ids = ops.argmax(logits)
+            ops.argmax(logits, out=out[:B])
+            out[B:].copy_(st.runtime.status)
         launches = ops.launch_count() - n0
         graph.replay()                                       # same tokens again: rewrites the same cache entries
         st.finish(ctx)
-        return _Captured(graph, buffer, logits, ids, launches)
+        stages = [torch.empty(total, dtype=torch.int32).pin_memory() for _ in range(2)]
+        for s in stages:
+            s.copy_(buffer)                                  # both start as the captured step's description
+        torch.cuda.current_stream().synchronize()
+        key = tuple(slots)
+        return _Captured(graph, buffer, offsets, sizes, stages, [None, None], [key, key], logits, out,
+                         torch.empty(B + 1, dtype=torch.int32).pin_memory(), launches)
 
-    @staticmethod
-    def _buffer_size(ctx: StepContext) -> int:
-        n = 0
-        for t in [ctx.token_ids, ctx.token_seq, ctx.token_pos, ctx.cu_seqlens, ctx.slots, ctx.kv_lens, ctx.logit_rows,
-                  *ctx.tables]:
-            n += (t.numel() + 3) // 4 * 4
-        return n
-
-    def step_and_sample(self, slots, tokens, streams, counters, recent, sampler) -> torch.Tensor:
-        logits, ids = self.step(slots, tokens)
+    # -- used by the generation loop -------------------------------------------------------------
+    def step_and_sample(self, slots, tokens, streams, counters, recent, sampler) -> List[int]:
         o = sampler.options
         if o.greedy and (o.rep_pen == 1.0 or not any(len(r) for r in recent)):
+            _, ids = self.step_to_host(slots, tokens)
             return ids
-        return sampler.sample(logits, streams, counters, recent)
+        logits, _ = self.step(slots, tokens)
+        host = sampler.sample(logits, streams, counters, recent).cpu()
+        self.stepper.check_status()
+        return host.tolist()
