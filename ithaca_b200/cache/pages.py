@@ -95,6 +95,7 @@ class SlotTable:
         self._in_use = np.zeros(max_slots, dtype=bool)
         self.length = np.zeros(max_slots, dtype=np.int64)             # positions each slot holds
         self._reserved = np.zeros(max_slots, dtype=np.int64)           # positions that have pages
+        self.epoch = np.zeros(max_slots, dtype=np.int64)               # how often each slot has been handed out
         # tables[g][slot, i] = page of positions [i*page_size, (i+1)*page_size), -1 = none
         self._cols = 4
         self.tables = [np.full((max_slots, self._cols), -1, dtype=np.int32) for _ in kv_groups]
@@ -108,6 +109,7 @@ class SlotTable:
         if self._in_use[s]:
             raise CacheError(f"slot {s} was on the free list while in use")
         self._in_use[s] = True
+        self.epoch[s] += 1
         self.length[s] = 0
         self._reserved[s] = 0
         for g in range(len(self.kv_groups)):

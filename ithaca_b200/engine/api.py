@@ -75,14 +75,22 @@ class Engine:
         return eng
 
     # -- the step function ---------------------------------------------------------------------
+    def _settle(self) -> None:
+        """Anything that touches the cache first drops the decode step that may have been launched ahead."""
+        if self._decoder is not None:
+            self._decoder.flush()
+
     def alloc_slot(self) -> int:
+        self._settle()
         return self.cache.alloc_slot()
 
     def free_slot(self, slot: int) -> None:
+        self._settle()
         self.cache.free_slot(slot)
 
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
              want: Union[str, None, Sequence[Sequence[int]]] = "last") -> Optional[torch.Tensor]:
+        self._settle()
         return self.stepper.step(slots, tokens, want)
 
     # -- Backend of the generation loop --------------------------------------------------------
@@ -97,6 +105,7 @@ class Engine:
     def step_and_sample(self, slots, tokens, streams, counters, recent) -> List[int]:
         if self._decoder is not None and all(len(t) == 1 for t in tokens):
             return self._decoder.step_and_sample(slots, tokens, streams, counters, recent, self._sampler)
+        self._settle()
         logits = self.stepper.step(slots, tokens, "last")
         host = self._sampler.sample(logits, streams, counters, recent).cpu()      # waits for the step
         self.stepper.check_status()
@@ -113,7 +122,10 @@ class Engine:
         elif kw:
             raise ValueError("give either options or keyword arguments")
         self._sampler = Sampler(options.sampling(), self.runtime.device)
-        out, stats = generate_loop(prompts, options, self, stop_token_ids=self.model.spec.stop_token_ids,
-                                   on_token=on_token)
+        try:
+            out, stats = generate_loop(prompts, options, self, stop_token_ids=self.model.spec.stop_token_ids,
+                                       on_token=on_token)
+        finally:
+            self._settle()
         self.last_stats = stats
         return out

@@ -10,6 +10,12 @@ refilled before each replay, so the same graph serves every step of that shape.
 The graph covers the forward pass, the greedy pick, and a copy of the kernels'
 status word next to the picked ids, so that one read-back per step brings both.
 
+In the greedy generation loop the next step is launched before the current one has been read
+back: its token ids are fed on the device from the current step's picks, so the GPU does not
+wait for the host between steps.  If the host then decides otherwise (a sequence ended, the
+caller asks for something else), the step launched ahead is dropped and the lengths it advanced
+are taken back; what it wrote lies beyond those lengths and is never read.
+
 The host side of a replayed step is kept short: the description is written
 straight into one of two pinned staging buffers (the other may still be in
 flight), only the fields that change from step to step are rewritten, and the
@@ -41,9 +47,20 @@ class _Captured:
     stage_slots: List[Optional[Tuple[int, ...]]]
     logits: torch.Tensor
     out: torch.Tensor                    # device int32 [B + 1]: greedy ids, then the status word
-    host_out: torch.Tensor               # pinned copy of ``out``
     launches: int
     turn: int = 0
+
+
+@dataclass
+class _Launched:
+    """A decode step that has been put on the stream and not yet read back."""
+    cap: _Captured
+    slots: Tuple[int, ...]
+    epochs: np.ndarray
+    new_lengths: np.ndarray
+    host_out: torch.Tensor               # pinned [B + 1]: greedy ids, then the status word
+    done: torch.cuda.Event
+    input_tokens: Optional[List[int]]    # the tokens this step was given (None until known: fed on the device)
 
 
 def _bucket(cols: int) -> int:
@@ -59,58 +76,126 @@ class GraphDecoder:
         self.stepper = stepper
         self.graphs: Dict[Tuple[int, int], _Captured] = {}
         self.launches_last_step = 0
-        self._read_back = torch.cuda.Event()
         self.last_upload_bytes = 0
+        self._ahead: Optional[_Launched] = None          # the step launched before its tokens reached the host
+        self._host_bufs: Dict[int, List[torch.Tensor]] = {}
+        self._host_turn = 0
+        self.steps_dropped = 0
 
     # -- one decode step -------------------------------------------------------------------------
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]]) -> Tuple[torch.Tensor, torch.Tensor]:
         """One token per slot.  Returns (logits [B, vocab], greedy ids [B]) on the device; both are
         the graph's own buffers and are overwritten by the next step of the same shape."""
-        cap = self._run(slots, tokens)
+        self.flush()
+        cap = self._run(slots, [t[0] for t in self._check_tokens(tokens)], None, strict=True)
         return cap.logits, cap.out[:len(slots)]
 
-    def step_to_host(self, slots: Sequence[int], tokens: Sequence[Sequence[int]]) -> Tuple[torch.Tensor, List[int]]:
-        """As ``step``, then waits for the step and returns (logits on the device, greedy ids on the
-        host).  Raises if a kernel reported an index out of range during the step."""
-        cap = self._run(slots, tokens)
-        cap.host_out.copy_(cap.out, non_blocking=True)
-        self._read_back.record()
-        self._read_back.synchronize()
-        got = cap.host_out.tolist()
-        if got[-1] != 0:
-            self.stepper.check_status()
-        return cap.logits, got[:-1]
+    def flush(self) -> None:
+        """Drops the step that was launched ahead, if any: the positions it added are taken back."""
+        a, self._ahead = self._ahead, None
+        if a is None:
+            return
+        table = self.stepper.cache.table
+        for i, s in enumerate(a.slots):
+            if table._in_use[s] and table.epoch[s] == a.epochs[i] and table.length[s] == a.new_lengths[i]:
+                table.length[s] -= 1
+        self.steps_dropped += 1
 
-    def _run(self, slots, tokens) -> _Captured:
+    def _check_tokens(self, tokens):
+        if any(len(t) != 1 for t in tokens):
+            raise StepError("a decode step brings exactly one token per slot")
+        return tokens
+
+    def _host_buffer(self, n: int) -> torch.Tensor:
+        bufs = self._host_bufs.get(n)
+        if bufs is None:
+            bufs = [torch.empty(n, dtype=torch.int32).pin_memory() for _ in range(3)]
+            self._host_bufs[n] = bufs
+        self._host_turn = (self._host_turn + 1) % 3
+        return bufs[self._host_turn]
+
+    def _launch(self, slots, tokens: Optional[List[int]], feed: Optional[_Captured], strict: bool) -> Optional[_Launched]:
+        table = self.stepper.cache.table
+        idx = np.asarray(slots, dtype=np.int64)
+        cap = self._run(slots, tokens, feed, strict)
+        if cap is None:
+            return None
+        host = self._host_buffer(len(slots) + 1)
+        host.copy_(cap.out, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return _Launched(cap, tuple(slots), table.epoch[idx].copy(), table.length[idx].copy(), host, ev, tokens)
+
+    def greedy_step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]]) -> List[int]:
+        """One greedy decode step: returns the picked ids on the host.  The following step is put on
+        the stream before this one is read back."""
+        toks = [int(t[0]) for t in self._check_tokens(tokens)]
+        key = tuple(slots)
+        cur, self._ahead = self._ahead, None
+        if cur is not None:
+            table = self.stepper.cache.table
+            idx = np.asarray(cur.slots, dtype=np.int64)
+            same = (cur.slots == key and cur.input_tokens == toks and bool((table.epoch[idx] == cur.epochs).all())
+                    and bool((table.length[idx] == cur.new_lengths).all()))
+            if not same:
+                self._ahead = cur
+                self.flush()
+                cur = None
+        if cur is None:
+            cur = self._launch(slots, toks, None, strict=True)
+        nxt = None
+        if not any(g.window is not None for g in self.stepper.cache.kv_groups):
+            nxt = self._launch(slots, None, cur.cap, strict=False)      # tokens: this step's picks, on the device
+        cur.done.synchronize()
+        got = cur.host_out.tolist()
+        if got[-1] != 0:
+            self._ahead = nxt
+            self.flush()
+            self.stepper.check_status()
+        if nxt is not None:
+            nxt.input_tokens = got[:-1]
+            self._ahead = nxt
+        return got[:-1]
+
+    def _run(self, slots, tokens: Optional[List[int]], feed: Optional[_Captured], strict: bool) -> Optional[_Captured]:
+        """Puts one decode step on the stream.  ``tokens``: host token ids, or None to take the ids
+        ``feed`` picked (on the device).  Not ``strict``: returns None instead of raising, with nothing
+        changed, when the step cannot run (no page left, a sequence at its limit, no graph yet)."""
         st = self.stepper
         table = st.cache.table
         page = st.cache.page_size
         B = len(slots)
-        if B == 0 or len(tokens) != B:
-            raise StepError("one token per slot is needed")
-        idx = np.asarray(slots, dtype=np.int64)
-        if idx.min() < 0 or idx.max() >= table.max_slots or not table._in_use[idx].all():
-            raise StepError("a slot of this step is not in use")
-        if len(set(slots)) != B:
-            raise StepError("a slot appears twice in one step")
-        toks = np.fromiter((t[0] for t in tokens), dtype=np.int64, count=B)
-        if any(len(t) != 1 for t in tokens):
-            raise StepError("a decode step brings exactly one token per slot")
-        if toks.min() < 0 or toks.max() >= st.vocab_size:
-            raise StepError(f"a token id is outside the vocabulary [0, {st.vocab_size})")
-        lens = table.length[idx]
-        if int(lens.max()) + 1 > st.max_position:
-            raise StepError(f"a sequence would exceed the model's limit of {st.max_position} positions")
-        cols = _bucket(int(-(-(int(lens.max()) + 1) // page)))
-        cap = self.graphs.get((B, cols))
-        if cap is None:
-            cap = self._capture(slots, tokens, cols)
-            self.graphs[(B, cols)] = cap
-            self.launches_last_step = cap.launches
-            return cap
-        # pages: a sequence needs a new one only when it stands at a page boundary
-        for s in idx[table._reserved[idx] <= lens]:
-            table.reserve(int(s), 1)
+        try:
+            if B == 0 or (tokens is not None and len(tokens) != B):
+                raise StepError("one token per slot is needed")
+            idx = np.asarray(slots, dtype=np.int64)
+            if idx.min() < 0 or idx.max() >= table.max_slots or not table._in_use[idx].all():
+                raise StepError("a slot of this step is not in use")
+            if len(set(slots)) != B:
+                raise StepError("a slot appears twice in one step")
+            if tokens is not None:
+                toks = np.asarray(tokens, dtype=np.int64)
+                if toks.min() < 0 or toks.max() >= st.vocab_size:
+                    raise StepError(f"a token id is outside the vocabulary [0, {st.vocab_size})")
+            lens = table.length[idx].copy()
+            if int(lens.max()) + 1 > st.max_position:
+                raise StepError(f"a sequence would exceed the model's limit of {st.max_position} positions")
+            cols = _bucket(int(-(-(int(lens.max()) + 1) // page)))
+            cap = self.graphs.get((B, cols))
+            if cap is None:
+                if tokens is None:
+                    return None                               # a new shape is captured with real tokens only
+                cap = self._capture(slots, [[t] for t in tokens], cols)
+                self.graphs[(B, cols)] = cap
+                self.launches_last_step = cap.launches
+                return cap
+            # pages: a sequence needs a new one only when it stands at a page boundary
+            for s in idx[table._reserved[idx] <= lens]:
+                table.reserve(int(s), 1)
+        except (StepError, CacheError):
+            if strict:
+                raise
+            return None
         # the description, into the staging buffer that is not in flight
         cap.turn ^= 1
         k = cap.turn
@@ -118,7 +203,8 @@ class GraphDecoder:
             cap.stage_events[k].synchronize()
         sn = cap.stages[k].numpy()
         o = cap.offsets
-        sn[o[0]:o[0] + B] = toks
+        if tokens is not None:
+            sn[o[0]:o[0] + B] = toks
         sn[o[2]:o[2] + B] = lens
         sn[o[5]:o[5] + B] = lens + 1
         key = tuple(slots)
@@ -139,6 +225,8 @@ class GraphDecoder:
         if cap.stage_events[k] is None:
             cap.stage_events[k] = torch.cuda.Event()
         cap.stage_events[k].record()
+        if tokens is None:
+            cap.buffer[o[0]:o[0] + B].copy_(feed.out[:B])      # the previous step's picks, device to device
         self.last_upload_bytes = cap.buffer.numel() * 4
         cap.graph.replay()
         # the sequences are one position longer
@@ -180,15 +268,13 @@ class GraphDecoder:
             s.copy_(buffer)                                  # both start as the captured step's description
         torch.cuda.current_stream().synchronize()
         key = tuple(slots)
-        return _Captured(graph, buffer, offsets, sizes, stages, [None, None], [key, key], logits, out,
-                         torch.empty(B + 1, dtype=torch.int32).pin_memory(), launches)
+        return _Captured(graph, buffer, offsets, sizes, stages, [None, None], [key, key], logits, out, launches)
 
     # -- used by the generation loop -------------------------------------------------------------
     def step_and_sample(self, slots, tokens, streams, counters, recent, sampler) -> List[int]:
         o = sampler.options
         if o.greedy and (o.rep_pen == 1.0 or not any(len(r) for r in recent)):
-            _, ids = self.step_to_host(slots, tokens)
-            return ids
+            return self.greedy_step(slots, tokens)
         logits, _ = self.step(slots, tokens)
         host = sampler.sample(logits, streams, counters, recent).cpu()
         self.stepper.check_status()

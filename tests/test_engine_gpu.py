@@ -105,3 +105,55 @@ def test_unequal_batches_with_slot_reuse(models, name, dtype):
             assert rel_err(np.concatenate(got[i], 0), refs[i]) <= REL[dtype], (lens, i)
     assert eng.cache.table.n_slots_in_use() == 0
     assert all(p.n_free == p.n_pages for p in eng.cache.table.pools)
+
+
+def test_llama_8b_layer_sizes_match_plain():
+    """Two layers with the sizes of Llama-3.1-8B (hidden 4096, 32/8 heads of 128, feed-forward 14336,
+    llama3 rotary scaling) and a cut vocabulary: every kernel at the sizes the benchmark runs
+    (split-K tcgen05 products, deep-unrolled skinny products, head size 128 attention), against the
+    plain implementation.  Prompt, then tokens one by one, in a batch of three unequal requests."""
+    from ithaca_b200 import Engine
+    from ithaca_b200.config import config_from_dict
+    from ithaca_b200.engine.model import weight_manifest
+    from ithaca_b200.weights import random_tensors
+    cfg = {"architectures": ["LlamaForCausalLM"], "hidden_size": 4096, "num_hidden_layers": 2, "num_attention_heads": 32,
+           "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336, "vocab_size": 2003, "rope_theta": 500000.0,
+           "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                            "original_max_position_embeddings": 8192},
+           "rms_norm_eps": 1e-5, "max_position_embeddings": 8192, "tie_word_embeddings": False, "torch_dtype": "bfloat16"}
+    tensors = random_tensors(weight_manifest(config_from_dict(cfg)[1].model_spec()), 5, "bfloat16")
+    reqs = [random_ids(n, 2003, 60 + n) for n in (40, 21, 70)]
+    refs = [plain_logits(cfg, tensors, r) for r in reqs]
+    for dtype in ("bfloat16", "float32"):
+        eng = Engine.from_random(cfg, 5, dtype=dtype, max_tokens=1024)
+        # from_random on the device draws other values than the CPU generator: load the CPU tensors instead
+        from ithaca_b200.engine.model import DecoderModel
+        eng.model = DecoderModel(eng.model.spec, tensors, eng.runtime)
+        eng.stepper.model = eng.model
+        slots = [eng.alloc_slot() for _ in reqs]
+        cut = [len(r) - 6 for r in reqs]
+        lg = eng.step(slots, [r[:c] for r, c in zip(reqs, cut)], "all").cpu().numpy()
+        got, off = [], 0
+        for c in cut:
+            got.append([lg[off:off + c]])
+            off += c
+        for t in range(6):
+            if dtype == "bfloat16":
+                lgd, _ = eng._decoder.step(slots, [[r[c + t]] for r, c in zip(reqs, cut)])
+            else:
+                lgd = eng.step(slots, [[r[c + t]] for r, c in zip(reqs, cut)], "last")
+            lgd = lgd.cpu().numpy()
+            for i in range(len(reqs)):
+                got[i].append(lgd[i:i + 1].copy())
+        eng.stepper.check_status()
+        for i in range(len(reqs)):
+            assert rel_err(np.concatenate(got[i]), refs[i]) <= REL[dtype], (dtype, i)
+        # a batch of 40 sequences takes the tcgen05 decode path (more than 16 tokens)
+        if dtype == "bfloat16":
+            many = [eng.alloc_slot() for _ in range(40)]
+            eng.step(many, [reqs[0][:30]] * 40, None)
+            lgd, _ = eng._decoder.step(many, [[reqs[0][30]]] * 40)
+            lgd = lgd.cpu().numpy()
+            assert rel_err(lgd, np.repeat(refs[0][30:31], 40, 0)) <= REL[dtype]
+        del eng
+        torch.cuda.empty_cache()
