@@ -125,7 +125,7 @@ def test_llama_8b_layer_sizes_match_plain():
     reqs = [random_ids(n, 2003, 60 + n) for n in (40, 21, 70)]
     refs = [plain_logits(cfg, tensors, r) for r in reqs]
     for dtype in ("bfloat16", "float32"):
-        eng = Engine.from_random(cfg, 5, dtype=dtype, max_tokens=1024)
+        eng = Engine.from_random(cfg, 5, dtype=dtype, max_tokens=64 * 64)
         # from_random on the device draws other values than the CPU generator: load the CPU tensors instead
         from ithaca_b200.engine.model import DecoderModel
         eng.model = DecoderModel(eng.model.spec, tensors, eng.runtime)
