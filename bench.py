@@ -29,6 +29,21 @@ LLAMA_3_1_8B = {
                                              "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
     "rms_norm_eps": 1e-5, "max_position_embeddings": 131072, "tie_word_embeddings": False, "torch_dtype": "bfloat16",
 }
+LLAMA_3_2_1B = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 2048, "num_hidden_layers": 16, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192, "vocab_size": 128256, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "max_position_embeddings": 131072, "tie_word_embeddings": True, "torch_dtype": "bfloat16",
+}
+LLAMA_2_13B = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 5120, "num_hidden_layers": 40, "num_attention_heads": 40,
+    "num_key_value_heads": 40, "head_dim": 128, "intermediate_size": 13824, "vocab_size": 32000, "rope_theta": 10000.0,
+    "rope_scaling": None, "rms_norm_eps": 1e-5, "max_position_embeddings": 4096 + 64, "tie_word_embeddings": False,
+    "torch_dtype": "bfloat16",
+}
+SHAPES = {"8b": ("Llama-3.1-8B shape", LLAMA_3_1_8B), "1b": ("Llama-3.2-1B shape", LLAMA_3_2_1B),
+          "13b": ("Llama-2-13B shape", LLAMA_2_13B)}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -186,6 +201,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES),
+                    help="layer sizes: 8b is the benchmark's configuration, the others are for comparison")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="run one part only and print its figures (for profiling a small case)")
@@ -205,13 +222,18 @@ def main():
     from ithaca_b200 import Engine
 
     pk = peaks()
-    cfg = dict(LLAMA_3_1_8B)
+    shape_name, shape_cfg = SHAPES[args.shape]
+    cfg = dict(shape_cfg)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
     n_layers = cfg["num_hidden_layers"]
     vocab = cfg["vocab_size"]
-    max_b = args.batch if (args.no_points or args.only != "all") else max(args.batch, 64)
+    point_batches = [] if (args.no_points or args.only != "all") else [1, 64]
+    # the cache of the largest batch has to fit beside the weights (bounded on purpose: no memory sweep)
+    per_token = 2 * 2 * n_layers * cfg["num_key_value_heads"] * cfg["head_dim"]
+    point_batches = [b for b in point_batches if b * (CONTEXT + 64) * per_token < 100e9]
+    max_b = max([args.batch] + point_batches)
     eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max_b * (CONTEXT + 64), ctx=CONTEXT + 64)
 
     if args.only == "decode":
@@ -226,8 +248,8 @@ def main():
     clocks = ClockSampler()
     main_run = decode_run(eng, args.batch, args.steps, args.warmup, vocab, CONTEXT, clocks)
     points = {}
-    if not args.no_points:
-        for b in (1, 64):
+    if point_batches:
+        for b in point_batches:
             points[f"decode_b{b}"] = round(decode_run(eng, b, min(args.steps, 32), args.warmup, vocab, CONTEXT)["tok_s"], 1)
     e2e = e2e_run(eng, args.batch, min(args.steps, 32), vocab, CONTEXT)
     pre_ms = prefill_run(eng, PREFILL_TOKENS, vocab)
@@ -239,12 +261,11 @@ def main():
     kv_bytes = eng.cache.bytes_per_token() * main_run["kv_len"] * args.batch
     achieved = (weight_bytes + kv_bytes) / (main_run["ms_per_step"] / 1e3) / 1e9
     line = {
-        "metric": "decode tok/s @ batch 8, context 4096 (Llama-3.1-8B shape)" if args.batch == 8 else
-                  f"decode tok/s @ batch {args.batch}, context 4096 (Llama-3.1-8B shape)",
+        "metric": f"decode tok/s @ batch {args.batch}, context 4096 ({shape_name})",
         "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",
-        "config": {"model": "Llama-3.1-8B shape", "layers": n_layers, "layers_of_model": full_layers,
+        "config": {"model": shape_name, "layers": n_layers, "layers_of_model": full_layers,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": vocab, "global_batch": args.batch,
