@@ -20,6 +20,7 @@
 // and is not followed.
 #include <math.h>
 #include "common.cuh"
+#include "tc_common.cuh"
 
 #ifndef IK_HD
 #error "compile with -DIK_HD=<head size>"
@@ -222,6 +223,245 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
             *reinterpret_cast<uint32_t*>(orow + d * 8 + 2 * t) = pack_bf16(o[d][2 * r] * inv, o[d][2 * r + 1] * inv);
     }
 }
+
+// ------------------------------------------------------------------------------------------ prefill, tcgen05
+// The same attention on the fifth-generation tensor cores, for head sizes 64 and 128.
+// A block owns 128 query tokens of one head of one sequence (one TMEM lane per query) and walks
+// the sequence's pages, 64 keys at a time:
+//   warp 0      TMA: the query tile once, then each page's keys and values into a 3-stage ring.
+//   warp 1      tcgen05.mma: S = Q K^T into one of two 64-column score buffers in TMEM (the product for
+//               page i + 1 is issued before the softmax of page i is done), then O += P V with P read
+//               from shared memory and V as an N-contiguous operand straight from the page.
+//   warps 2..5  softmax: each thread reads its query's 64 scores from TMEM, masks by position, keeps
+//               the running maximum and sum in float (base 2), rescales its row of O in TMEM when the
+//               maximum moved, writes P as bfloat16 into shared memory in the operand's swizzled layout.
+// All mbarrier waits are bounded (tc_common.cuh); on a timeout the status word is set and the block
+// leaves its loops and frees its TMEM.
+#if IK_HD == 64 || IK_HD == 128
+constexpr int TC_BM = 128, TC_NS = 3;
+constexpr int TC_BOXES = HD / 64;                              // 64-wide swizzled blocks along the head size
+constexpr int TC_Q_BYTES = TC_BM * HD * 2;
+constexpr int TC_KV_BYTES = PAGE * HD * 2;
+constexpr int TC_P_BYTES = TC_BM * PAGE * 2;
+constexpr int TC_SMEM = TC_Q_BYTES + TC_NS * 2 * TC_KV_BYTES + TC_P_BYTES + 1024 + 256;
+constexpr int TC_TMEM_COLS = 256;                              // scores 2 x 64, output HD (<= 128)
+constexpr int TC_O_COL = 128;
+
+__global__ void __launch_bounds__(192, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
+                       const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,
+                       const int* __restrict__ table, int table_stride, int nh, int nkv, float scale_log2e,
+                       int window, int n_pages, int* status) {
+    extern __shared__ unsigned char tc_smem[];
+    ik_pdl_launch_dependents();
+    ik_pdl_wait();
+    const int b = blockIdx.z, h = blockIdx.y, tile = blockIdx.x;
+    const int q_begin = cu_seqlens[b], n_new = cu_seqlens[b + 1] - q_begin;
+    const int row0 = tile * TC_BM;
+    if (row0 >= n_new) return;
+    if (status && *(volatile int*)status == IK_STATUS_GEMM_TIMEOUT) return;
+    const int kv_len = kv_lens[b], start = kv_len - n_new;
+    const int rows = min(TC_BM, n_new - row0);
+    const int pos_lo = start + row0, pos_hi = pos_lo + rows - 1;
+    const int j_lo = (window > 0 && pos_lo + 1 > window) ? pos_lo + 1 - window : 0;
+    const int p_lo = j_lo / PAGE, n_iter = pos_hi / PAGE - p_lo + 1;
+    const int kvh = h / (nh / nkv);
+
+    unsigned char* base = (unsigned char*)(((uintptr_t)tc_smem + 1023) & ~(uintptr_t)1023);
+    unsigned char* Qs = base;
+    unsigned char* Ks = Qs + TC_Q_BYTES;                       // [TC_NS][TC_KV_BYTES]
+    unsigned char* Vs = Ks + TC_NS * TC_KV_BYTES;
+    unsigned char* Ps = Vs + TC_NS * TC_KV_BYTES;
+    uint64_t* q_full = (uint64_t*)(Ps + TC_P_BYTES);
+    uint64_t* k_full = q_full + 1;                             // [TC_NS]
+    uint64_t* v_full = k_full + TC_NS;
+    uint64_t* kv_free = v_full + TC_NS;
+    uint64_t* s_full = kv_free + TC_NS;                        // [2]
+    uint64_t* p_ready = s_full + 2;
+    uint64_t* pv_done = p_ready + 1;
+    uint32_t* tmem_slot = (uint32_t*)(pv_done + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < TC_NS; s++) { mbar_init(k_full + s, 1); mbar_init(v_full + s, 1); mbar_init(kv_free + s, 1); }
+        mbar_init(s_full, 1); mbar_init(s_full + 1, 1);
+        mbar_init(p_ready, 128);
+        mbar_init(pv_done, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" :: "l"(&map_q) : "memory");
+        asm volatile("prefetch.tensormap [%0];" :: "l"(&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" :: "l"(&map_v) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(smem_u32(tmem_slot)), "r"((uint32_t)TC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(q_full, TC_Q_BYTES);
+            for (int bx = 0; bx < TC_BOXES; bx++)
+                tma_load_2d(Qs + bx * (TC_BM * 128), &map_q, h * HD + bx * 64, q_begin + row0, q_full);
+            for (int i = 0; i < n_iter; i++) {
+                const int s = i % TC_NS;
+                if (!mbar_wait(kv_free + s, ((i / TC_NS) & 1) ^ 1, abort_flag, status)) break;
+                int page = table[(size_t)b * table_stride + p_lo + i];
+                if (page < 0 || page >= n_pages) { if (status) atomicExch(status, 3); page = 0; }
+                const int row = (page * nkv + kvh) * PAGE;
+                mbar_expect_tx(k_full + s, TC_KV_BYTES);
+                for (int bx = 0; bx < TC_BOXES; bx++)
+                    tma_load_2d(Ks + s * TC_KV_BYTES + bx * (PAGE * 128), &map_k, bx * 64, row, k_full + s);
+                mbar_expect_tx(v_full + s, TC_KV_BYTES);
+                for (int bx = 0; bx < TC_BOXES; bx++)
+                    tma_load_2d(Vs + s * TC_KV_BYTES + bx * (PAGE * 128), &map_v, bx * 64, row, v_full + s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_qk = umma_idesc(PAGE), idesc_pv = umma_idesc(HD, 1);
+            const uint32_t q_addr = smem_u32(Qs), p_addr = smem_u32(Ps);
+            bool ok = mbar_wait(q_full, 0, abort_flag, status);
+            auto issue_qk = [&](int i) -> bool {
+                const int s = i % TC_NS;
+                if (!mbar_wait(k_full + s, (i / TC_NS) & 1, abort_flag, status)) return false;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t k_addr = smem_u32(Ks + s * TC_KV_BYTES);
+                #pragma unroll
+                for (int j = 0; j < HD / 16; j++)
+                    umma(tmem + (i & 1) * PAGE, umma_desc(q_addr + (j / 4) * (TC_BM * 128) + (j % 4) * 32),
+                         umma_desc(k_addr + (j / 4) * (PAGE * 128) + (j % 4) * 32), idesc_qk, j != 0);
+                umma_commit(s_full + (i & 1));
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int i = 0; i < n_iter && ok; i++) {
+                if (i + 1 < n_iter) { ok = issue_qk(i + 1); if (!ok) break; }     // runs while page i is in the softmax
+                const int s = i % TC_NS;
+                ok = mbar_wait(p_ready, i & 1, abort_flag, status) && mbar_wait(v_full + s, (i / TC_NS) & 1, abort_flag, status);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t v_addr = smem_u32(Vs + s * TC_KV_BYTES);
+                #pragma unroll
+                for (int j = 0; j < PAGE / 16; j++)
+                    umma(tmem + TC_O_COL, umma_desc(p_addr + j * 32), umma_desc_mn(v_addr + j * 2048, PAGE * 128), idesc_pv,
+                         (i | j) != 0);
+                umma_commit(kv_free + s);
+                umma_commit(pv_done);
+            }
+        }
+    } else {
+        const int quarter = warp & 3, r = quarter * 32 + lane;
+        const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+        const bool row_valid = r < rows;
+        const int pos_r = pos_lo + r;
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int i = 0; i < n_iter && ok; i++) {
+            const int p = p_lo + i;
+            ok = mbar_wait(s_full + (i & 1), (i >> 1) & 1, abort_flag, status);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float sc[PAGE];
+            #pragma unroll
+            for (int c0 = 0; c0 < PAGE; c0 += 16) {
+                float v[16];
+                tmem_ld16(lane_base + (i & 1) * PAGE + c0, v);
+                #pragma unroll
+                for (int c = 0; c < 16; c++) sc[c0 + c] = v[c];
+            }
+            const bool need_mask = (p * PAGE + PAGE - 1 > pos_lo) || (window > 0 && p * PAGE < pos_hi + 1 - window);
+            float mx = -INFINITY;
+            if (need_mask) {
+                #pragma unroll
+                for (int c = 0; c < PAGE; c++) {
+                    const int j = p * PAGE + c;
+                    const bool in = row_valid && j <= pos_r && (window <= 0 || j > pos_r - window);
+                    sc[c] = in ? sc[c] * scale_log2e : -INFINITY;
+                    mx = fmaxf(mx, sc[c]);
+                }
+            } else {
+                #pragma unroll
+                for (int c = 0; c < PAGE; c++) {
+                    sc[c] = row_valid ? sc[c] * scale_log2e : -INFINITY;
+                    mx = fmaxf(mx, sc[c]);
+                }
+            }
+            const float m_new = fmaxf(m, mx);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = exp2f(m - m_use);
+            float sum = 0.f;
+            #pragma unroll
+            for (int c = 0; c < PAGE; c++) { sc[c] = exp2f(sc[c] - m_use); sum += sc[c]; }
+            l = l * alpha + sum;
+            m = m_new;
+            if (i > 0) {
+                ok = mbar_wait(pv_done, (i - 1) & 1, abort_flag, status);         // O and the P buffer are free again
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (__any_sync(0xffffffffu, alpha != 1.f)) {
+                    #pragma unroll
+                    for (int c0 = 0; c0 < HD; c0 += 16) {
+                        float v[16];
+                        tmem_ld16(lane_base + TC_O_COL + c0, v);
+                        #pragma unroll
+                        for (int c = 0; c < 16; c++) v[c] *= alpha;
+                        tmem_st16(lane_base + TC_O_COL + c0, v);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            // this query's 64 probabilities, as a row of the swizzled K-major operand
+            unsigned char* prow = Ps + r * 128;
+            #pragma unroll
+            for (int c = 0; c < 8; c++) {
+                uint4 w;
+                w.x = pack_bf16(sc[c * 8 + 0], sc[c * 8 + 1]);
+                w.y = pack_bf16(sc[c * 8 + 2], sc[c * 8 + 3]);
+                w.z = pack_bf16(sc[c * 8 + 4], sc[c * 8 + 5]);
+                w.w = pack_bf16(sc[c * 8 + 6], sc[c * 8 + 7]);
+                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) * 16)) = w;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");         // visible to the tensor core's reads
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(p_ready);
+        }
+        if (ok && mbar_wait(pv_done, (n_iter - 1) & 1, abort_flag, status)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float inv = 1.0f / l;
+            bf16* orow = out + ((size_t)(q_begin + row0 + r) * nh + h) * HD;
+            #pragma unroll
+            for (int c0 = 0; c0 < HD; c0 += 16) {
+                float v[16];
+                tmem_ld16(lane_base + TC_O_COL + c0, v);
+                if (row_valid) {
+                    uint4 w0, w1;
+                    w0.x = pack_bf16(v[0] * inv, v[1] * inv);   w0.y = pack_bf16(v[2] * inv, v[3] * inv);
+                    w0.z = pack_bf16(v[4] * inv, v[5] * inv);   w0.w = pack_bf16(v[6] * inv, v[7] * inv);
+                    w1.x = pack_bf16(v[8] * inv, v[9] * inv);   w1.y = pack_bf16(v[10] * inv, v[11] * inv);
+                    w1.z = pack_bf16(v[12] * inv, v[13] * inv); w1.w = pack_bf16(v[14] * inv, v[15] * inv);
+                    *reinterpret_cast<uint4*>(orow + c0) = w0;
+                    *reinterpret_cast<uint4*>(orow + c0 + 8) = w1;
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"((uint32_t)TC_TMEM_COLS) : "memory");
+    }
+}
+#endif  // head sizes 64 and 128
 
 // ------------------------------------------------------------------------------------------ decode
 // One block: (sequence, kv head, up to 16 of the group's query heads, one chunk of pages).
@@ -452,6 +692,35 @@ IK_EXPORT int ik_attn_prefill(const void* q, const void* k_pages, const void* v_
                                           cu_seqlens, kv_lens, table, table_stride, nh, nkv,
                                           scale * 1.4426950408889634f, window, n_pages, status));
     IK_LAUNCH_STATUS();
+}
+
+// The tcgen05 kernel (head sizes 64 and 128; IK_UNSUPPORTED otherwise).  T: rows of q.
+IK_EXPORT int ik_attn_prefill_tc(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_seqlens,
+                                 const int* kv_lens, const int* table, int table_stride, int T, int B, int max_new, int nh,
+                                 int nkv, float scale, int window, int page_size, int n_pages, int* status,
+                                 cudaStream_t stream) {
+#if IK_HD == 64 || IK_HD == 128
+    if (T <= 0 || B <= 0 || max_new <= 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size != PAGE || B > 65535 || nh > 65535)
+        return IK_BAD_ARGUMENT;
+    if (((uintptr_t)q % 16) || ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16)) return IK_UNSUPPORTED;
+    CUtensorMap mq, mk, mv;
+    int st = ik_make_map(&mq, q, (unsigned long long)T, nh * HD, (unsigned long long)nh * HD, TC_BM);
+    if (st != IK_OK) return st;
+    const unsigned long long kv_rows = (unsigned long long)n_pages * nkv * PAGE;
+    st = ik_make_map(&mk, k_pages, kv_rows, HD, HD, PAGE);
+    if (st != IK_OK) return st;
+    st = ik_make_map(&mv, v_pages, kv_rows, HD, HD, PAGE);
+    if (st != IK_OK) return st;
+    auto kern = attn_prefill_tc_kernel;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid((max_new + TC_BM - 1) / TC_BM, nh, B);
+    IK_RETURN_IF_ERROR(ik_launch(kern, grid, 192, TC_SMEM, stream, mq, mk, mv, (bf16*)out, cu_seqlens, kv_lens, table,
+                                 table_stride, nh, nkv, scale * 1.4426950408889634f, window, n_pages, status));
+    IK_LAUNCH_STATUS();
+#else
+    return IK_UNSUPPORTED;
+#endif
 }
 
 // part_o: [B, nh, n_splits, HD] floats, part_ml: [B, nh, n_splits, 2] floats, both owned by the caller.

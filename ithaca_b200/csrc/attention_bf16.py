@@ -43,6 +43,8 @@ def module(head_dim: int) -> ctypes.CDLL:
         m = build.load_library(f"ithaca_attn_hd{head_dim}", ["attention_bf16.cu"], defines=[f"IK_HD={head_dim}"])
         m.ik_attn_prefill.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp]
         m.ik_attn_prefill.restype = _i
+        m.ik_attn_prefill_tc.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp]
+        m.ik_attn_prefill_tc.restype = _i
         m.ik_attn_decode.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _i, _i, _i, _i,
                                      _vp, _vp]
         m.ik_attn_decode.restype = _i
@@ -54,11 +56,23 @@ def module(head_dim: int) -> ctypes.CDLL:
 
 def prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, cu_seqlens: torch.Tensor,
             kv_lens: torch.Tensor, table: torch.Tensor, n_seqs: int, max_new: int, n_heads: int, scale: float,
-            window: int, status: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+            window: int, status: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
+            kind: str = "auto") -> torch.Tensor:
+    """``kind``: "tc" = the tcgen05 kernel (head sizes 64 and 128), "mma" = the warp-level kernel,
+    "auto" = tcgen05 where it applies."""
     n_pages, nkv, page_size, hd = k_pages.shape
     m = module(hd)
     if out is None:
         out = torch.empty_like(q)
+    if kind == "tc" or (kind == "auto" and hd in (64, 128)):
+        st = m.ik_attn_prefill_tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(cu_seqlens), _ptr(kv_lens),
+                                  _ptr(table), table.stride(0), q.shape[0], n_seqs, max_new, n_heads, nkv, scale, window,
+                                  page_size, n_pages, _ptr(status), _stream())
+        if st != -2:
+            _check(st, "attention prefill (tcgen05)")
+            return out
+        if kind == "tc":
+            raise KernelError("attention prefill (tcgen05): head size or alignment not supported")
     _check(m.ik_attn_prefill(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(cu_seqlens), _ptr(kv_lens),
                              _ptr(table), table.stride(0), n_seqs, max_new, n_heads, nkv, scale, window, page_size,
                              n_pages, _ptr(status), _stream()), "attention prefill")

@@ -23,10 +23,7 @@
 // every role leaves its loop; TMEM is freed and the block returns.  Blocks that start after
 // the status word is set return at once.  Needs K % 8 == 0 and 16-byte aligned rows (TMA
 // strides); the host entry returns IK_UNSUPPORTED otherwise.
-#include <cuda.h>
-#include "common.cuh"
-
-#define IK_STATUS_GEMM_TIMEOUT 4
+#include "tc_common.cuh"
 
 namespace {
 
@@ -35,91 +32,6 @@ constexpr int BM = 128;              // weight rows per tile = TMEM lanes
 constexpr int BK = 64;               // 64 bf16 = 128 bytes = one swizzle row
 constexpr int THREADS = 192;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ unsigned long long globaltimer() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Waits for the phase with the given parity to complete.  Gives up after ~1 s (or as soon as
-// another thread of the block has given up) and returns false.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
-    if (mbar_test(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer();
-    for (int spin = 0;; spin++) {
-        if (mbar_test(bar, parity)) return true;
-        if ((spin & 63) == 63) {
-            if (*abort_flag) return false;
-            if (globaltimer() - t0 > 1000000000ull) {
-                *abort_flag = 1;
-                if (status) atomicExch(status, IK_STATUS_GEMM_TIMEOUT);
-                return false;
-            }
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        :: "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle, groups of
-// 8 rows 1024 bytes apart (version 1 = sm_100).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address
-    d |= (uint64_t)1 << 16;                               // leading byte offset (unused under swizzle) = 1
-    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                               // descriptor version
-    d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
-    return d;
-}
-// Instruction descriptor: D float, A and B bfloat16, both K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t umma_idesc(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                 :: "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-    #pragma unroll
-    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
-}
-
 template <int BN> struct Cfg {
     static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE = A_BYTES + B_BYTES;
     static constexpr int STAGES = (200 * 1024 / STAGE) > 8 ? 8 : (200 * 1024 / STAGE);
@@ -127,10 +39,6 @@ template <int BN> struct Cfg {
     static constexpr int TMEM_COLS = 2 * ACC_COLS;               // two accumulators: one is drained while the other fills
     static constexpr int SMEM = STAGES * STAGE + 1024 /* alignment slack */ + 256 /* barriers */;
 };
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(bar)) : "memory");
-}
 
 // map_w: [N rows, K] box {64, 128};  map_x: [M rows, K] box {64, BN}.
 // out: Y (float or bf16) when partial == nullptr, else partial sums [splits][M][N] float.
@@ -330,36 +238,6 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TY* __re
     }
 }
 
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-    static EncodeTiled fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiled)p;
-    }
-    return fn;
-}
-
-// rows x K bfloat16 matrix, K contiguous, row stride ld elements; box = 64 x box_rows, 128-byte swizzle, zero fill.
-int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
-    EncodeTiled enc = encode_fn();
-    if (!enc) return IK_UNSUPPORTED;
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? IK_OK : IK_BAD_ARGUMENT;
-}
-
 template <int BN, typename TY>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial, int M, int N, int K, int ldy,
            int accumulate, int swiglu, int splits, int* status, cudaStream_t stream) {
@@ -405,9 +283,9 @@ IK_EXPORT int ik_gemm_tcgen05(const void* X, const void* W, void* Y, int y_dtype
     if (M == 0) return IK_OK;
     const int bn = ik_gemm_tcgen05_tile(M);
     CUtensorMap mw, mx;
-    int st = make_map(&mw, W, N, K, ldw, BM);
+    int st = ik_make_map(&mw, W, N, K, ldw, BM);
     if (st != IK_OK) return st;
-    st = make_map(&mx, X, M, K, ldx, bn);
+    st = ik_make_map(&mx, X, M, K, ldx, bn);
     if (st != IK_OK) return st;
 #define IK_TC(BN_)                                                                                                       \
     return y_dtype == IK_F32 ? launch<BN_, float>(mw, mx, Y, partial, M, N, K, ldy, accumulate, swiglu, splits, status, stream) \

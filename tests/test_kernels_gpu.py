@@ -286,16 +286,17 @@ def test_attention_simt(nh, nkv, hd, window, dtype):
     close(got, c["ref"], 3e-6 if dtype == torch.float32 else 8e-3)
 
 
-@pytest.mark.parametrize("nh,nkv,hd", SHAPES)
+@pytest.mark.parametrize("nh,nkv,hd,kind", [s + ("mma",) for s in SHAPES] + [(8, 2, 64, "tc"), (8, 4, 128, "tc"),
+                                                                            (4, 4, 128, "tc")])
 @pytest.mark.parametrize("window", [0, 40, 100])
-def test_attention_bf16_prefill(nh, nkv, hd, window):
+def test_attention_bf16_prefill(nh, nkv, hd, kind, window):
     from ithaca_b200.csrc import attention_bf16 as A
-    lens, new = [1, 70, 200, 129, 64], [1, 70, 67, 129, 5]       # whole prompts and later chunks
+    lens, new = [1, 70, 200, 129, 64, 700], [1, 70, 67, 129, 5, 450]       # whole prompts and later chunks
     c = attention_case(nh, nkv, hd, lens, new, window or None, torch.bfloat16, seed=31)
     k_d, v_d, tab = c["pg"].dev()
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     got = A.prefill(c["q"], k_d, v_d, c["cu"], c["kv_lens"], tab, len(lens), max(new), nh, 1 / math.sqrt(hd), window,
-                    status)
+                    status, kind=kind)
     assert status.item() == 0
     close(got, c["ref"], 8e-3)
 
@@ -316,7 +317,7 @@ def test_attention_bf16_decode(nh, nkv, hd, window):
         close(got, c["ref"], 8e-3)
 
 
-@pytest.mark.parametrize("kind", ["simt32", "prefill", "decode"])
+@pytest.mark.parametrize("kind", ["simt32", "prefill", "prefill_tc", "decode"])
 def test_attention_reaches_a_far_key_and_respects_the_window_edge(kind):
     """One key far back is made to dominate the last query's scores: the output must be that
     key's value.  Under a window the same key just outside must not count, just inside must."""
@@ -337,8 +338,9 @@ def test_attention_reaches_a_far_key_and_respects_the_window_edge(kind):
         scale = 1 / math.sqrt(hd)
         if kind == "simt32":
             got = ops().attention_simt(c["q"], k_d, v_d, c["token_seq"], c["token_pos"], tab, nh, scale, window, status)
-        elif kind == "prefill":
-            got = A.prefill(c["q"], k_d, v_d, c["cu"], c["kv_lens"], tab, 1, n_new, nh, scale, window, status)
+        elif kind in ("prefill", "prefill_tc"):
+            got = A.prefill(c["q"], k_d, v_d, c["cu"], c["kv_lens"], tab, 1, n_new, nh, scale, window, status,
+                            kind="mma" if kind == "prefill" else "tc")
         else:
             got = A.decode(c["q"], k_d, v_d, c["kv_lens"], tab, 1, L, nh, scale, window, status)
         close(got, c["ref"], 3e-6 if dtype == torch.float32 else 8e-3)
