@@ -238,25 +238,26 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
 // All mbarrier waits are bounded (tc_common.cuh); on a timeout the status word is set and the block
 // leaves its loops and frees its TMEM.
 #if IK_HD == 64 || IK_HD == 128
-constexpr int TC_BM = 128, TC_NS = 3;
+constexpr int TC_BM = 128, TC_NS = 2;                          // two blocks per SM: one's softmax runs beside the other's MMAs
 constexpr int TC_BOXES = HD / 64;                              // 64-wide swizzled blocks along the head size
 constexpr int TC_Q_BYTES = TC_BM * HD * 2;
 constexpr int TC_KV_BYTES = PAGE * HD * 2;
 constexpr int TC_P_BYTES = TC_BM * PAGE * 2;
-constexpr int TC_SMEM = TC_Q_BYTES + TC_NS * 2 * TC_KV_BYTES + TC_P_BYTES + 1024 + 256;
+constexpr int TC_SMEM = TC_Q_BYTES + TC_NS * 2 * TC_KV_BYTES + TC_P_BYTES + 256;   // no slack: see the alignment check
 constexpr int TC_TMEM_COLS = 256;                              // scores 2 x 64, output HD (<= 128)
 constexpr int TC_O_COL = 128;
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
                        const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,
                        const int* __restrict__ table, int table_stride, int nh, int nkv, float scale_log2e,
                        int window, int n_pages, int* status) {
-    extern __shared__ unsigned char tc_smem[];
+    extern __shared__ __align__(1024) unsigned char tc_smem[];
     ik_pdl_launch_dependents();
     ik_pdl_wait();
-    const int b = blockIdx.z, h = blockIdx.y, tile = blockIdx.x;
+    // late tiles see the most keys: they are started first, so that the short ones fill the tail
+    const int b = blockIdx.z, h = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
     const int q_begin = cu_seqlens[b], n_new = cu_seqlens[b + 1] - q_begin;
     const int row0 = tile * TC_BM;
     if (row0 >= n_new) return;
@@ -268,8 +269,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int p_lo = j_lo / PAGE, n_iter = pos_hi / PAGE - p_lo + 1;
     const int kvh = h / (nh / nkv);
 
-    unsigned char* base = (unsigned char*)(((uintptr_t)tc_smem + 1023) & ~(uintptr_t)1023);
-    unsigned char* Qs = base;
+    // The swizzled tiles need 1024-byte alignment.  Dynamic shared memory of a kernel without static shared
+    // memory starts on such a boundary; should it ever not, the block reports it instead of computing garbage.
+    if (smem_u32(tc_smem) & 1023) {
+        if (threadIdx.x == 0 && status) atomicExch(status, 5);
+        return;
+    }
+    unsigned char* Qs = tc_smem;
     unsigned char* Ks = Qs + TC_Q_BYTES;                       // [TC_NS][TC_KV_BYTES]
     unsigned char* Vs = Ks + TC_NS * TC_KV_BYTES;
     unsigned char* Ps = Vs + TC_NS * TC_KV_BYTES;
@@ -372,49 +378,56 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float sc[PAGE];
             #pragma unroll
-            for (int c0 = 0; c0 < PAGE; c0 += 16) {
-                float v[16];
-                tmem_ld16(lane_base + (i & 1) * PAGE + c0, v);
-                #pragma unroll
-                for (int c = 0; c < 16; c++) sc[c0 + c] = v[c];
-            }
+            for (int c0 = 0; c0 < PAGE; c0 += 16) tmem_ld16_issue(lane_base + (i & 1) * PAGE + c0, sc + c0);
+            tmem_ld_wait();
             const bool need_mask = (p * PAGE + PAGE - 1 > pos_lo) || (window > 0 && p * PAGE < pos_hi + 1 - window);
-            float mx = -INFINITY;
+            // four independent chains for the maximum (and below for the sum): one warp per scheduler has
+            // nothing else to hide the latency of a dependent chain behind
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (need_mask) {
                 #pragma unroll
                 for (int c = 0; c < PAGE; c++) {
                     const int j = p * PAGE + c;
                     const bool in = row_valid && j <= pos_r && (window <= 0 || j > pos_r - window);
                     sc[c] = in ? sc[c] * scale_log2e : -INFINITY;
-                    mx = fmaxf(mx, sc[c]);
+                    mx4[c & 3] = fmaxf(mx4[c & 3], sc[c]);
                 }
             } else {
                 #pragma unroll
                 for (int c = 0; c < PAGE; c++) {
                     sc[c] = row_valid ? sc[c] * scale_log2e : -INFINITY;
-                    mx = fmaxf(mx, sc[c]);
+                    mx4[c & 3] = fmaxf(mx4[c & 3], sc[c]);
                 }
             }
-            const float m_new = fmaxf(m, mx);
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = exp2f(m - m_use);
-            float sum = 0.f;
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // m is the reference the exponentials are taken against.  It follows the running maximum only when
+            // that has moved by more than 8 (a factor 256): until then the probabilities may exceed 1 by that
+            // factor, which float sums and bfloat16 operands take in their stride, and O needs no rescaling.
+            float alpha = 1.f;
+            if (mx > m + 8.f) {
+                alpha = ik_ex2(m - mx);                                          // 0 on the first page (m = -inf)
+                m = mx;
+            }
+            const float m_use = m == -INFINITY ? 0.f : m;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             #pragma unroll
-            for (int c = 0; c < PAGE; c++) { sc[c] = exp2f(sc[c] - m_use); sum += sc[c]; }
-            l = l * alpha + sum;
-            m = m_new;
+            for (int c = 0; c < PAGE; c++) { sc[c] = ik_ex2(sc[c] - m_use); sum4[c & 3] += sc[c]; }
+            l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             if (i > 0) {
                 ok = mbar_wait(pv_done, (i - 1) & 1, abort_flag, status);         // O and the P buffer are free again
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (__any_sync(0xffffffffu, alpha != 1.f)) {
                     #pragma unroll
-                    for (int c0 = 0; c0 < HD; c0 += 16) {
-                        float v[16];
-                        tmem_ld16(lane_base + TC_O_COL + c0, v);
+                    for (int c0 = 0; c0 < HD; c0 += 32) {
+                        float v[32];
+                        tmem_ld16_issue(lane_base + TC_O_COL + c0, v);
+                        tmem_ld16_issue(lane_base + TC_O_COL + c0 + 16, v + 16);
+                        tmem_ld_wait();
                         #pragma unroll
-                        for (int c = 0; c < 16; c++) v[c] *= alpha;
-                        tmem_st16(lane_base + TC_O_COL + c0, v);
+                        for (int c = 0; c < 32; c++) v[c] *= alpha;
+                        tmem_st16(lane_base + TC_O_COL + c0, *reinterpret_cast<float(*)[16]>(v));
+                        tmem_st16(lane_base + TC_O_COL + c0 + 16, *reinterpret_cast<float(*)[16]>(v + 16));
                     }
                     tmem_st_wait();
                 }

@@ -118,6 +118,12 @@ def build_library(name: str, sources: Sequence[str], defines: Sequence[str] = ()
         tmp = so + f".tmp{os.getpid()}"
         _run([nvcc, *_ARCH_FLAGS, "-shared", "-o", tmp, *objs, *[f"-l{l}" for l in libs]], f"lib{name}")
         os.replace(tmp, so)
+        for old in os.listdir(out_dir):                     # builds of earlier versions of these sources
+            if old.startswith(f"lib{name}_") and old.endswith(".so") and old != os.path.basename(so):
+                try:
+                    os.remove(os.path.join(out_dir, old))
+                except OSError:
+                    pass
     finally:
         shutil.rmtree(work, ignore_errors=True)
     _log(f"{name} ready in {time.time() - t0:.1f} s")
@@ -143,6 +149,12 @@ def core() -> ctypes.CDLL:
     return load_library("ithaca_kernels", CORE_SOURCES)
 
 
+ATTENTION_HEAD_SIZES = (16, 32, 48, 64, 128)     # the sizes the tests and the benchmark use; others compile on demand
+
+
 def build_all() -> None:
-    """Everything that can be compiled ahead of time."""
+    """Everything that can be compiled ahead of time: the core library and the attention module of
+    every usual head size."""
     core()
+    for hd in ATTENTION_HEAD_SIZES:
+        build_library(f"ithaca_attn_hd{hd}", ["attention_bf16.cu"], defines=[f"IK_HD={hd}"])

@@ -108,5 +108,6 @@ class Stepper:
                 st.zero_()
                 what = {1: "a token id outside the vocabulary", 2: "a cache write without a page",
                         3: "a cache read without a page",
-                        4: "a matrix-product block that gave up waiting for its data"}.get(v, f"code {v}")
+                        4: "a matrix-product block that gave up waiting for its data",
+                        5: "shared memory that is not aligned for the tensor-core tiles"}.get(v, f"code {v}")
                 raise CacheError(f"a kernel reported {what}")

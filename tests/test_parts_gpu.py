@@ -95,6 +95,56 @@ def test_attention_part_prompt_then_tokens(dtype, window):
     assert rel_err(out.double().cpu().numpy(), ref.numpy()) <= (3e-6 if dtype == "float32" else 1e-2)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_block_arrangement(dtype, tmp_path):
+    """One pre-norm block alone: x += attention(norm(x)); x += feed_forward(norm(x)), fed a residual stream
+    of the test's own making, against the plain parts in the same order."""
+    from ithaca_b200.cache import SequenceCache
+    from ithaca_b200.config import config_from_model_dir
+    from ithaca_b200.engine.context import ContextBuilder
+    from ithaca_b200.parts import BLOCKS
+    from ithaca_b200.weights import read_model_tensors
+    d = make_model_dir(tmp_path, TINY_B, seed=6)
+    pcfg, pt = load_plain(d)
+    _, cfg = config_from_model_dir(d)
+    spec = cfg.model_spec().layers[1]
+    rt = runtime(dtype)
+    block = BLOCKS.get(spec.kind)(spec, read_model_tensors(d), rt)
+    cache = SequenceCache({0: block.cache_requests()}, max_tokens=128, kv_dtype=rt.kv_dtype, device=DEV)
+    slot = cache.alloc_slot()
+    T = 50
+    x = torch.randn(T, 192) * 0.5
+    res = x.to(DEV).clone()
+    cache.reserve([slot], [T])
+    ctx = ContextBuilder(DEV).build([slot], [[0] * T], [0], [[]], [cache.table.table_rows(0, [slot], 1)])
+    block.forward(res, ctx, cache.layer(0), True)
+    c = P.normalized_config(pcfg)
+    p = "model.layers.1"
+    xd = x.double()
+    xn = P.rmsnorm(xd, pt[f"{p}.input_layernorm.weight"], c["rms_norm_eps"])
+    xd = xd + P.attention_block(xn, pt, f"{p}.self_attn", c, P.rope_inv_freq(c["head_dim"], c["rope_theta"], c["rope_scaling"]),
+                                torch.arange(T))
+    xn = P.rmsnorm(xd, pt[f"{p}.post_attention_layernorm.weight"], c["rms_norm_eps"])
+    xd = xd + P.gated_mlp(xn, pt[f"{p}.mlp.gate_proj.weight"], pt[f"{p}.mlp.up_proj.weight"], pt[f"{p}.mlp.down_proj.weight"])
+    assert rt.status.item() == 0
+    assert rel_err(res.double().cpu().numpy(), xd.numpy()) <= (3e-6 if dtype == "float32" else 5e-3)
+
+
+def test_embedding_and_head_parts():
+    from ithaca_b200.config import PartSpec
+    from ithaca_b200.parts.embedding import Embedding, OutputHead
+    rt = runtime("bfloat16")
+    table = (torch.randn(301, 72) * 0.1).to(torch.bfloat16)
+    emb = Embedding(PartSpec("embedding", {"vocab_size": 301, "hidden_size": 72, "scale": 1.0}, {"weight": "e"}), {"e": table}, rt)
+    ids = torch.tensor([5, 300, 0], dtype=torch.int32, device=DEV)
+    assert torch.equal(emb.forward(ids).cpu(), table.float()[[5, 300, 0]])
+    head = OutputHead(PartSpec("lm_head", {"vocab_size": 301, "hidden_size": 72, "tied": True}, {"weight": "e"}), {"e": emb.table}, rt)
+    assert head.linear.weight.data_ptr() == emb.table.data_ptr()                # a tied head shares the table on the device
+    xn = (torch.randn(4, 72)).to(torch.bfloat16)
+    got = head.forward(xn.to(DEV)).double().cpu()
+    assert rel_err(got.numpy(), (xn.double() @ table.double().T).numpy()) <= 2e-5
+
+
 def test_schedule_names_a_layer_twice_and_shares_a_cache(tmp_path):
     """The order of runs is data.  Layer 0 runs twice with caches of its own; a last run of layer 1
     reads the cache its first run filled.  The plain side spells the same order out by hand."""
