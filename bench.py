@@ -251,7 +251,7 @@ def main():
     if point_batches:
         for b in point_batches:
             points[f"decode_b{b}"] = round(decode_run(eng, b, min(args.steps, 32), args.warmup, vocab, CONTEXT)["tok_s"], 1)
-    e2e = e2e_run(eng, args.batch, min(args.steps, 32), vocab, CONTEXT)
+    e2e = e2e_run(eng, args.batch, args.steps, vocab, CONTEXT)
     pre_ms = prefill_run(eng, PREFILL_TOKENS, vocab)
 
     layer_flops, head_flops = model_flops_per_token(cfg, n_layers)

@@ -31,6 +31,16 @@ __device__ __forceinline__ float ik_ld(const __nv_bfloat16* p, size_t i) { retur
 __device__ __forceinline__ void ik_st(float* p, size_t i, float v) { p[i] = v; }
 __device__ __forceinline__ void ik_st(__nv_bfloat16* p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
 
+// Four consecutive values (16-byte aligned source, 8- or 16-byte aligned destination).
+__device__ __forceinline__ void ik_st4(float* p, size_t i, float4 v) { *reinterpret_cast<float4*>(p + i) = v; }
+__device__ __forceinline__ void ik_st4(__nv_bfloat16* p, size_t i, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 w;
+    w.x = *reinterpret_cast<uint32_t*>(&lo);
+    w.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p + i) = w;
+}
+
 // silu(g) * u with silu(x) = x / (1 + exp(-x)).
 __device__ __forceinline__ float ik_swiglu(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 // The same with the hardware's approximate exp and reciprocal (relative error ~1e-6), for results that are

@@ -114,15 +114,16 @@ rope_append_kernel(const float* __restrict__ qkv, TQ* __restrict__ q_out, TC* __
                    const int* __restrict__ table, int table_stride, const float* __restrict__ inv_freq, int nh, int nkv,
                    int hd, int rot, int pairing, int page_size, int n_pages, int write_cache, int heads_per_block,
                    int* status) {
-    extern __shared__ float cs[];                  // [rot/2] cos, then [rot/2] sin of this token's angles
+    extern __shared__ __align__(16) float cs[];    // [rot/2] cos, then [rot/2] sin of this token's angles
     ik_pdl_launch_dependents();
     ik_pdl_wait();
-    const int t = blockIdx.x, half = rot / 2;
+    // threads: x runs over a head's elements, y over heads (no division in the loops)
+    const int t = blockIdx.x, half = rot / 2, tid = threadIdx.y * blockDim.x + threadIdx.x;
     const int head_lo = blockIdx.y * heads_per_block;                          // over q heads, then k heads, then v heads
     const int head_hi = min(head_lo + heads_per_block, nh + 2 * nkv);
     const int pos = token_pos[t];
     if (head_lo < nh + nkv) {
-        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        for (int i = tid; i < half; i += blockDim.x * blockDim.y) {
             const float ang = __fmul_rn((float)pos, inv_freq[i]);
             cs[i] = cosf(ang);
             cs[half + i] = sinf(ang);
@@ -134,43 +135,61 @@ rope_append_kernel(const float* __restrict__ qkv, TQ* __restrict__ q_out, TC* __
     if (write_cache && head_hi > nh) {
         const int page = table[(size_t)token_seq[t] * table_stride + pos / page_size];
         page_ok = page >= 0 && page < n_pages;
-        if (!page_ok) { if (threadIdx.x == 0 && status) atomicExch(status, 2); }       // never write outside the pool
+        if (!page_ok) { if (tid == 0 && status) atomicExch(status, 2); }               // never write outside the pool
         else page_off = ((size_t)page * nkv * page_size + (pos % page_size)) * hd;
     }
     __syncthreads();
     const float* src = qkv + (size_t)t * (nh + 2 * nkv) * hd;
-    const int n_heads = head_hi - head_lo;
-    // rotated pairs of the q and k heads of this block
-    for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
-        const int head = head_lo + idx / half, i = idx % half;
-        if (head >= nh + nkv) break;                                           // v heads follow; handled below
-        const bool is_q = head < nh;
-        if (!is_q && !page_ok) continue;
-        const int i0 = pairing == 0 ? i : 2 * i, i1 = pairing == 0 ? i + half : 2 * i + 1;
-        const float c = cs[i], sn = cs[half + i];
-        const float a = src[(size_t)head * hd + i0], b = src[(size_t)head * hd + i1];
-        const float r0 = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn));
-        const float r1 = __fadd_rn(__fmul_rn(a, sn), __fmul_rn(b, c));
-        if (is_q) {
-            const size_t o = ((size_t)t * nh + head) * hd;
-            ik_st(q_out, o + i0, r0);
-            ik_st(q_out, o + i1, r1);
-        } else {
-            const size_t o = page_off + (size_t)(head - nh) * page_size * hd;
-            ik_st(k_pages, o + i0, r0);
-            ik_st(k_pages, o + i1, r1);
-        }
-    }
-    // dimensions beyond the rotated width pass through; value heads are copied whole
-    for (int idx = threadIdx.x; idx < n_heads * hd; idx += blockDim.x) {
-        const int head = head_lo + idx / hd, i = idx % hd;
+    // four pairs per thread where the layout allows 16-byte accesses (half-split pairs, widths in fours)
+    const bool vec = pairing == 0 && (half & 3) == 0 && (hd & 3) == 0 && (((nh + 2 * nkv) * hd) & 3) == 0;
+    for (int head = head_lo + threadIdx.y; head < head_hi; head += blockDim.y) {
+        const float* hsrc = src + (size_t)head * hd;
         if (head < nh + nkv) {
-            if (i < rot) continue;
-            const float v = src[(size_t)head * hd + i];
-            if (head < nh) ik_st(q_out, ((size_t)t * nh + head) * hd + i, v);
-            else if (page_ok) ik_st(k_pages, page_off + (size_t)(head - nh) * page_size * hd + i, v);
-        } else if (page_ok) {
-            ik_st(v_pages, page_off + (size_t)(head - nh - nkv) * page_size * hd + i, src[(size_t)head * hd + i]);
+            const bool is_q = head < nh;
+            if (!is_q && !page_ok) continue;
+            TQ* qdst = q_out + ((size_t)t * nh + head) * hd;
+            TC* kdst = k_pages + page_off + (size_t)(head - nh) * page_size * hd;
+            if (vec) {
+                for (int i = 4 * threadIdx.x; i < half; i += 4 * blockDim.x) {
+                    const float4 a = *reinterpret_cast<const float4*>(hsrc + i);
+                    const float4 b = *reinterpret_cast<const float4*>(hsrc + half + i);
+                    const float4 c = *reinterpret_cast<const float4*>(cs + i);
+                    const float4 sn = *reinterpret_cast<const float4*>(cs + half + i);
+                    float4 r0, r1;
+                    r0.x = __fsub_rn(__fmul_rn(a.x, c.x), __fmul_rn(b.x, sn.x)); r1.x = __fadd_rn(__fmul_rn(a.x, sn.x), __fmul_rn(b.x, c.x));
+                    r0.y = __fsub_rn(__fmul_rn(a.y, c.y), __fmul_rn(b.y, sn.y)); r1.y = __fadd_rn(__fmul_rn(a.y, sn.y), __fmul_rn(b.y, c.y));
+                    r0.z = __fsub_rn(__fmul_rn(a.z, c.z), __fmul_rn(b.z, sn.z)); r1.z = __fadd_rn(__fmul_rn(a.z, sn.z), __fmul_rn(b.z, c.z));
+                    r0.w = __fsub_rn(__fmul_rn(a.w, c.w), __fmul_rn(b.w, sn.w)); r1.w = __fadd_rn(__fmul_rn(a.w, sn.w), __fmul_rn(b.w, c.w));
+                    if (is_q) { ik_st4(qdst, i, r0); ik_st4(qdst, half + i, r1); }
+                    else { ik_st4(kdst, i, r0); ik_st4(kdst, half + i, r1); }
+                }
+                for (int i = rot + 4 * threadIdx.x; i < hd; i += 4 * blockDim.x) {     // beyond the rotated width
+                    const float4 v = *reinterpret_cast<const float4*>(hsrc + i);
+                    if (is_q) ik_st4(qdst, i, v);
+                    else ik_st4(kdst, i, v);
+                }
+                continue;
+            }
+            for (int i = threadIdx.x; i < half; i += blockDim.x) {                 // rotated pairs
+                const int i0 = pairing == 0 ? i : 2 * i, i1 = pairing == 0 ? i + half : 2 * i + 1;
+                const float c = cs[i], sn = cs[half + i];
+                const float a = hsrc[i0], b = hsrc[i1];
+                const float r0 = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn));
+                const float r1 = __fadd_rn(__fmul_rn(a, sn), __fmul_rn(b, c));
+                if (is_q) { ik_st(qdst, i0, r0); ik_st(qdst, i1, r1); }
+                else { ik_st(kdst, i0, r0); ik_st(kdst, i1, r1); }
+            }
+            for (int i = rot + threadIdx.x; i < hd; i += blockDim.x) {              // beyond the rotated width
+                if (is_q) ik_st(qdst, i, hsrc[i]);
+                else ik_st(kdst, i, hsrc[i]);
+            }
+        } else if (page_ok) {                                                       // a value head: copied whole
+            TC* vdst = v_pages + page_off + (size_t)(head - nh - nkv) * page_size * hd;
+            if (vec) {
+                for (int i = 4 * threadIdx.x; i < hd; i += 4 * blockDim.x) ik_st4(vdst, i, *reinterpret_cast<const float4*>(hsrc + i));
+            } else {
+                for (int i = threadIdx.x; i < hd; i += blockDim.x) ik_st(vdst, i, hsrc[i]);
+            }
         }
     }
 }
@@ -182,10 +201,10 @@ IK_EXPORT int ik_rope_append(const float* qkv, void* q_out, int q_dtype, void* k
     if (T < 0 || nh <= 0 || nkv <= 0 || hd <= 0 || rot < 0 || rot > hd || (rot & 1) || page_size <= 0) return IK_BAD_ARGUMENT;
     if (rot > 0 && !inv_freq) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
-    // few tokens (decode): spread a token's heads over several blocks; many tokens: one block per token
-    const int hpb = T >= 256 ? nh + 2 * nkv : 4;
+    // few tokens (decode): spread a token's heads over many blocks; many tokens: 16 heads a block
+    const int hpb = T >= 256 ? 16 : 4;
     dim3 grid(T, (nh + 2 * nkv + hpb - 1) / hpb);
-    const int threads = 256;
+    const dim3 threads(32, 8);
     const size_t smem = (size_t)rot * sizeof(float);
 #define IK_ROPE(TQ, TC)                                                                                             \
     IK_RETURN_IF_ERROR(ik_launch(rope_append_kernel<TQ, TC>, grid, threads, smem, stream, qkv, (TQ*)q_out, (TC*)k_pages, (TC*)v_pages, token_seq, \
