@@ -19,6 +19,7 @@
 // in the unused part of a page never matters.  A page index outside the pool sets *status
 // and is not followed.
 #include <math.h>
+#define IK_FAMILY 4
 #include "common.cuh"
 #include "tc_common.cuh"
 

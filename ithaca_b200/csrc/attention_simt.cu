@@ -8,6 +8,7 @@
 // function.  This is the 32-bit path's attention and the fallback for head sizes the
 // tensor-core kernels do not take.
 #include <math.h>
+#define IK_FAMILY 4
 #include "common.cuh"
 
 namespace {

@@ -89,7 +89,7 @@ __device__ __forceinline__ float ik_block_max(float v, float* scratch) {
 // L2), and only then waits for the predecessor's results.  The wait returns when every earlier
 // kernel has completed and its writes are visible, so nothing after it can race; nothing
 // before it may touch memory that other kernels write.  The launch attribute is off unless
-// IK_PDL=1 is in the environment (kernels then start strictly one after another and the
+// IK_PDL=<mask of kernel families> is in the environment (kernels then start strictly one after another and the
 // device-side calls are no-ops): on the decode step of the Llama-3.1-8B shape, replayed from a
 // CUDA graph, early launch measured no gain on B200.
 __device__ __forceinline__ void ik_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -99,24 +99,35 @@ __device__ __forceinline__ void ik_prefetch_l2(const void* p, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(p), "r"(bytes) : "memory");
 }
 
-static inline int ik_pdl_enabled() {
+// Kernel families, for IK_PDL=<bit mask>: which launches get the attribute.
+#define IK_FAMILY_ELEMENTWISE 1
+#define IK_FAMILY_SKINNY 2
+#define IK_FAMILY_ATTENTION 4
+#define IK_FAMILY_TCGEN05 8
+#define IK_FAMILY_SAMPLING 16
+#ifndef IK_FAMILY
+#define IK_FAMILY IK_FAMILY_ELEMENTWISE
+#endif
+
+static inline int ik_pdl_mask() {
     static int v = -1;
-    if (v < 0) { const char* e = getenv("IK_PDL"); v = e ? atoi(e) != 0 : 0; }
+    if (v < 0) { const char* e = getenv("IK_PDL"); v = e ? atoi(e) : 0; }
     return v;
 }
 
 template <typename... KArgs, typename... Args>
-static inline cudaError_t ik_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                    Args&&... args) {
+static inline cudaError_t ik_launch_family(int family, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                           cudaStream_t stream, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = ik_pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = (ik_pdl_mask() & family) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
+#define ik_launch(...) ik_launch_family(IK_FAMILY, __VA_ARGS__)
 
 #define IK_RETURN_IF_ERROR(...)                         \
     do {                                                \

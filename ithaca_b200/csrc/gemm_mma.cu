@@ -17,6 +17,7 @@
 // The order in which a result's K terms are added depends on K alone (and on which of the
 // two kernels runs), never on M or N.  Needs K % 8 == 0 and 16-byte aligned rows; the entry
 // points return IK_UNSUPPORTED otherwise and the caller uses the CUDA-core product.
+#define IK_FAMILY 2
 #include "common.cuh"
 
 namespace {

@@ -5,6 +5,7 @@
 // float accumulator that adds its K products in ascending k, whatever M and N are, so a
 // row of Y does not depend on which other rows are in the call.  No split along K, no
 // atomics, no reduced-precision matrix mode.
+#define IK_FAMILY 2
 #include "common.cuh"
 
 namespace {

@@ -23,6 +23,7 @@
 // every role leaves its loop; TMEM is freed and the block returns.  Blocks that start after
 // the status word is set return at once.  Needs K % 8 == 0 and 16-byte aligned rows (TMA
 // strides); the host entry returns IK_UNSUPPORTED otherwise.
+#define IK_FAMILY 8
 #include "tc_common.cuh"
 
 namespace {

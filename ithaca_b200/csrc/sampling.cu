@@ -12,6 +12,7 @@
 // are ordered by ascending id.  No sort is done anywhere: the k-th largest value and the
 // top_p boundary are found by bisection over the bits of an order-preserving integer key.
 #include <math.h>
+#define IK_FAMILY 16
 #include "common.cuh"
 
 namespace {
