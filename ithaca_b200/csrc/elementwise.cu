@@ -194,6 +194,28 @@ rope_append_kernel(const float* __restrict__ qkv, TQ* __restrict__ q_out, TC* __
     }
 }
 
+// cos_sin[t][i] = (cos, sin) of float(pos_t) * inv_freq_i: made once per step, used by every layer's fused
+// q/k/v epilogue.
+__global__ void rope_table_kernel(const int* __restrict__ token_pos, const float* __restrict__ inv_freq,
+                                  float* __restrict__ cos_sin, int T, int half) {
+    ik_pdl_launch_dependents();
+    ik_pdl_wait();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= T * half) return;
+    const int t = idx / half, i = idx - t * half;
+    const float ang = __fmul_rn((float)token_pos[t], inv_freq[i]);
+    cos_sin[2 * (size_t)idx] = cosf(ang);
+    cos_sin[2 * (size_t)idx + 1] = sinf(ang);
+}
+
+IK_EXPORT int ik_rope_table(const int* token_pos, const float* inv_freq, float* cos_sin, int T, int half,
+                            cudaStream_t stream) {
+    if (T < 0 || half <= 0) return IK_BAD_ARGUMENT;
+    if (T == 0) return IK_OK;
+    IK_RETURN_IF_ERROR(ik_launch(rope_table_kernel, (T * half + 255) / 256, 256, 0, stream, token_pos, inv_freq, cos_sin, T, half));
+    IK_LAUNCH_STATUS();
+}
+
 IK_EXPORT int ik_rope_append(const float* qkv, void* q_out, int q_dtype, void* k_pages, void* v_pages, int cache_dtype,
                              const int* token_seq, const int* token_pos, const int* table, int table_stride,
                              const float* inv_freq, int T, int nh, int nkv, int hd, int rot, int pairing,

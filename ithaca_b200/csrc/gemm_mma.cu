@@ -19,6 +19,7 @@
 // points return IK_UNSUPPORTED otherwise and the caller uses the CUDA-core product.
 #define IK_FAMILY 2
 #include "common.cuh"
+#include "rope_store.cuh"
 
 namespace {
 
@@ -52,7 +53,7 @@ __device__ __forceinline__ void store_out(__nv_bfloat16* Y, size_t o, float v, i
 template <int NT, int U, typename TY>
 __global__ void __launch_bounds__(256)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, TY* __restrict__ Y,
-                   int M, int N, int K, int ldx, int ldw, int ldy, int accumulate, int swiglu) {
+                   int M, int N, int K, int ldx, int ldw, int ldy, int accumulate, int swiglu, const IkRopeStore rope) {
     constexpr int R = 16, COLS = 8 * NT;
     extern __shared__ float red[];                       // [8 warps][R][COLS]
     ik_pdl_launch_dependents();
@@ -119,6 +120,21 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
         mine[(g + 8) * COLS + col + 1] = acc[n][3];
     }
     __syncthreads();
+    if (rope.q_out) {
+        // rows are rotary pairs of q and k heads, then v heads: rotate and store to q_out and the cache
+        for (int idx = threadIdx.x; idx < (R / 2) * COLS; idx += 256) {
+            const int m = idx / (R / 2), pr = idx % (R / 2);
+            if (m >= M || n0 + 2 * pr + 1 >= N) continue;
+            float a = 0.f, b = 0.f;
+            #pragma unroll
+            for (int w = 0; w < 8; w++) {
+                a += red[(size_t)w * R * COLS + (2 * pr) * COLS + m];
+                b += red[(size_t)w * R * COLS + (2 * pr + 1) * COLS + m];
+            }
+            ik_rope_store_pair(rope, m, n0 + 2 * pr, a, b);
+        }
+        return;
+    }
     if (swiglu) {
         // rows are (gate j, up j) pairs: Y[m, (n0 + row) / 2] = silu(gate) * up
         for (int idx = threadIdx.x; idx < (R / 2) * COLS; idx += 256) {
@@ -146,12 +162,12 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
 
 template <int NT, int U, typename TY>
 int launch_skinny(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
-                  int accumulate, int swiglu, cudaStream_t stream) {
+                  int accumulate, int swiglu, const IkRopeStore& rope, cudaStream_t stream) {
     constexpr int R = 16;
     const size_t smem = (size_t)8 * R * 8 * NT * sizeof(float);
     auto kern = gemm_skinny_kernel<NT, U, TY>;
     IK_RETURN_IF_ERROR(ik_launch(kern, (N + R - 1) / R, 256, smem, stream, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W,
-                                 (TY*)Y, M, N, K, ldx, ldw, ldy, accumulate, swiglu));
+                                 (TY*)Y, M, N, K, ldx, ldw, ldy, accumulate, swiglu, rope));
     IK_LAUNCH_STATUS();
 }
 
@@ -270,9 +286,9 @@ bool aligned_ok(const void* X, const void* W, int K, int ldx, int ldw) {
 
 // kind: 0 = choose by M (skinny for M <= 64, else tiled), 1 = skinny, 2 = tiled.
 // swiglu (skinny only): W holds (gate j, up j) in rows (2j, 2j + 1); Y is [M, N / 2] = silu(gate) * up.
-IK_EXPORT int ik_gemm_bf16_mma(const void* X, const void* W, void* Y, int y_dtype, int M, int N, int K, int ldx, int ldw,
-                               int ldy, int accumulate, int kind, int swiglu, cudaStream_t stream) {
-    if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || ldy < (swiglu ? N / 2 : N)) return IK_BAD_ARGUMENT;
+static int gemm_bf16_mma_impl(const void* X, const void* W, void* Y, int y_dtype, int M, int N, int K, int ldx, int ldw,
+                              int ldy, int accumulate, int kind, int swiglu, const IkRopeStore& rope, cudaStream_t stream) {
+    if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || (!rope.q_out && ldy < (swiglu ? N / 2 : N))) return IK_BAD_ARGUMENT;
     if (swiglu && ((N & 1) || accumulate || kind == 2 || (kind == 0 && M > 64))) return IK_BAD_ARGUMENT;
     if (y_dtype != IK_F32 && y_dtype != IK_BF16) return IK_BAD_ARGUMENT;
     if (!aligned_ok(X, W, K, ldx, ldw)) return IK_UNSUPPORTED;
@@ -280,8 +296,8 @@ IK_EXPORT int ik_gemm_bf16_mma(const void* X, const void* W, void* Y, int y_dtyp
     const bool skinny = kind == 1 || (kind == 0 && M <= 64);
     if (skinny && M > 64) return IK_UNSUPPORTED;
 #define IK_SK(NT, U)                                                                                           \
-    return y_dtype == IK_F32 ? launch_skinny<NT, U, float>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, swiglu, stream) \
-                             : launch_skinny<NT, U, __nv_bfloat16>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, swiglu, stream)
+    return y_dtype == IK_F32 ? launch_skinny<NT, U, float>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, swiglu, rope, stream) \
+                             : launch_skinny<NT, U, __nv_bfloat16>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, swiglu, rope, stream)
     if (skinny) {
         const bool deep = deep_unroll_pays(N);
         if (M <= 8) { if (deep) { IK_SK(1, 4); } IK_SK(1, 2); }
@@ -292,4 +308,18 @@ IK_EXPORT int ik_gemm_bf16_mma(const void* X, const void* W, void* Y, int y_dtyp
 #undef IK_SK
     return y_dtype == IK_F32 ? launch_tiled<float>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, stream)
                              : launch_tiled<__nv_bfloat16>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, stream);
+}
+
+IK_EXPORT int ik_gemm_bf16_mma(const void* X, const void* W, void* Y, int y_dtype, int M, int N, int K, int ldx, int ldw,
+                               int ldy, int accumulate, int kind, int swiglu, cudaStream_t stream) {
+    IkRopeStore none = {};
+    return gemm_bf16_mma_impl(X, W, Y, y_dtype, M, N, K, ldx, ldw, ldy, accumulate, kind, swiglu, none, stream);
+}
+
+// The fused q/k/v product of up to 64 tokens with the rotary / cache epilogue (rope_store.cuh).  N must be
+// (nh + 2 nkv) * hd, hd even.
+IK_EXPORT int ik_gemm_qkv_rope_mma(const void* X, const void* W, int M, int N, int K, int ldx, int ldw,
+                                   const IkRopeStore* rope, cudaStream_t stream) {
+    if (!rope || !rope->q_out || (rope->hd & 1) || N != (rope->nh + 2 * rope->nkv) * rope->hd || M > 64) return IK_BAD_ARGUMENT;
+    return gemm_bf16_mma_impl(X, W, nullptr, IK_F32, M, N, K, ldx, ldw, N, 0, 1, 0, *rope, stream);
 }

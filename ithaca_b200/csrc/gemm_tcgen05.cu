@@ -25,6 +25,7 @@
 // strides); the host entry returns IK_UNSUPPORTED otherwise.
 #define IK_FAMILY 8
 #include "tc_common.cuh"
+#include "rope_store.cuh"
 
 namespace {
 
@@ -53,9 +54,10 @@ template <int BN, typename TY>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     TY* __restrict__ Y, float* __restrict__ partial, int M, int N, int K, int ldy, int accumulate,
-                    int swiglu, int kb_per_split, int n_splits, int* status) {
+                    int swiglu, int kb_per_split, int n_splits, int* status, const IkRopeStore rope) {
     typedef Cfg<BN> C;
     extern __shared__ unsigned char smem_raw[];
+    __shared__ int rope_rows[4][BN];                   // per epilogue warp: the cache row of each of the tile's tokens
     ik_pdl_launch_dependents();
     if (status && *(volatile int*)status == IK_STATUS_GEMM_TIMEOUT) return;     // an earlier block gave up
     unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -151,19 +153,71 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     } else {
         // epilogue: warp w owns TMEM lanes 32 * (w % 4) .. + 31
         const int quarter = warp & 3;
+        const bool fused_rope = rope.q_out && !partial;
         int lt = 0;
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, lt++) {
             IK_TILE_COORDS(t)
             (void)kb0; (void)nkb;
             const int buf = lt & 1;
             const int feature = n0 + quarter * 32 + lane;
+            if (fused_rope) {
+                // each warp keeps its own list of the tile's cache rows (no barrier between warps is needed); the
+                // lookups run while the accumulator is still being filled
+                __syncwarp();
+                for (int i = lane; i < BN; i += 32) rope_rows[quarter][i] = ik_rope_cache_row(rope, m0 + i, M);
+                __syncwarp();
+            }
             if (!mbar_wait(acc_full + buf, (lt >> 1) & 1, abort_flag, status)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * C::ACC_COLS;
+            // what the rotary epilogue needs of this lane's feature pair: fixed for the whole tile
+            const int f0 = feature & ~1;
+            const int head = fused_rope ? f0 / rope.hd : 0, r0 = fused_rope ? f0 - head * rope.hd : 0;
+            const bool is_q = head < rope.nh, rotated = head < rope.nh + rope.nkv;
+            bf16* const kv_base = (rotated ? rope.k_pages : rope.v_pages) +
+                                  (size_t)(head - rope.nh - (rotated ? 0 : rope.nkv)) * rope.page_size * rope.hd + r0;
+            const float2* const cs_base = reinterpret_cast<const float2*>(rope.cos_sin) + (r0 >> 1);
             #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 if (m0 + c0 >= M) break;
                 float v[16];
+                if (fused_rope) {
+                    // lanes (2j, 2j + 1) hold a rotary pair (or two neighbouring values of a v head).  The pair shares
+                    // the work: the even lane takes columns 0..7, the odd lane columns 8..15.  All cosines and sines
+                    // are fetched before the accumulator is read and before any store, so that they are in flight
+                    // together (a store could alias them as far as the compiler knows).
+                    const bool odd = lane & 1;
+                    const int col0 = c0 + (odd ? 8 : 0);
+                    float2 cs[8];
+                    #pragma unroll
+                    for (int c = 0; c < 8; c++)
+                        cs[c] = rotated && feature < N && m0 + col0 + c < M
+                                    ? __ldg(cs_base + (size_t)(m0 + col0 + c) * (rope.hd >> 1)) : make_float2(1.f, 0.f);
+                    tmem_ld16(acc + c0, v);
+                    __nv_bfloat162 packed[8];
+                    #pragma unroll
+                    for (int c = 0; c < 8; c++) {
+                        const float other = __shfl_xor_sync(0xffffffffu, odd ? v[c] : v[c + 8], 1);
+                        const float a = odd ? other : v[c], b = odd ? v[c + 8] : other;
+                        packed[c] = __floats2bfloat162_rn(a * cs[c].x - b * cs[c].y, a * cs[c].y + b * cs[c].x);
+                    }
+                    if (feature < N) {
+                        if (is_q) {
+                            #pragma unroll
+                            for (int c = 0; c < 8; c++)
+                                if (m0 + col0 + c < M)
+                                    *reinterpret_cast<__nv_bfloat162*>(rope.q_out + (size_t)(m0 + col0 + c) * rope.nh * rope.hd + f0) = packed[c];
+                        } else {
+                            int rows[8];
+                            #pragma unroll
+                            for (int c = 0; c < 8; c++) rows[c] = rope_rows[quarter][col0 + c];
+                            #pragma unroll
+                            for (int c = 0; c < 8; c++)
+                                if (rows[c] >= 0) *reinterpret_cast<__nv_bfloat162*>(kv_base + (size_t)rows[c] * rope.hd) = packed[c];
+                        }
+                    }
+                    continue;
+                }
                 tmem_ld16(acc + c0, v);
                 if (feature < N || (swiglu && !partial)) {     // N is even under swiglu: a pair is in or out together
                     if (partial) {
@@ -212,10 +266,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // Adds the K slices in slice order and writes Y.
 template <typename TY>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TY* __restrict__ Y, int M, int N, int ldy,
-                                     int splits, int accumulate, int swiglu) {
+                                     int splits, int accumulate, int swiglu, const IkRopeStore rope) {
     ik_pdl_launch_dependents();
     ik_pdl_wait();
     const size_t total = (size_t)M * N;
+    if (rope.q_out) {                   // columns (2j, 2j + 1) are rotary pairs: rotate and store to q_out and the cache
+        const size_t half = (size_t)M * (N / 2);
+        for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < half; idx += (size_t)gridDim.x * blockDim.x) {
+            const size_t m = idx / (N / 2), j = idx - m * (N / 2);
+            float a = 0.f, b = 0.f;
+            for (int z = 0; z < splits; z++) {
+                a += partial[(size_t)z * total + m * N + 2 * j];
+                b += partial[(size_t)z * total + m * N + 2 * j + 1];
+            }
+            ik_rope_store_pair(rope, (int)m, (int)(2 * j), a, b);
+        }
+        return;
+    }
     if (swiglu) {                       // columns (2j, 2j + 1) are gate j and up j; Y is [M, N / 2]
         const size_t half = (size_t)M * (N / 2);
         for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < half; idx += (size_t)gridDim.x * blockDim.x) {
@@ -241,7 +308,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TY* __re
 
 template <int BN, typename TY>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial, int M, int N, int K, int ldy,
-           int accumulate, int swiglu, int splits, int* status, cudaStream_t stream) {
+           int accumulate, int swiglu, int splits, int* status, const IkRopeStore& rope, cudaStream_t stream) {
     typedef Cfg<BN> C;
     auto kern = gemm_tcgen05_kernel<BN, TY>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
@@ -252,13 +319,13 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial
     const long long total = (long long)((N + BM - 1) / BM) * ((M + BN - 1) / BN) * n_splits;
     const int blocks = (int)(total < 148 ? total : 148);
     IK_RETURN_IF_ERROR(ik_launch(kern, blocks, THREADS, C::SMEM, stream, mw, mx, (TY*)Y, n_splits > 1 ? partial : nullptr, M,
-                                 N, K, ldy, accumulate, swiglu, per, n_splits, status));
+                                 N, K, ldy, accumulate, swiglu, per, n_splits, status, rope));
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (n_splits > 1) {
         const size_t elems = (size_t)M * N;
         const int rblocks = (int)((elems + 255) / 256 < 148 * 8 ? (elems + 255) / 256 : 148 * 8);
-        IK_RETURN_IF_ERROR(ik_launch(splitk_reduce_kernel<TY>, rblocks, 256, 0, stream, partial, (TY*)Y, M, N, ldy, n_splits, accumulate, swiglu));
+        IK_RETURN_IF_ERROR(ik_launch(splitk_reduce_kernel<TY>, rblocks, 256, 0, stream, partial, (TY*)Y, M, N, ldy, n_splits, accumulate, swiglu, rope));
         e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
     }
@@ -273,10 +340,11 @@ IK_EXPORT int ik_gemm_tcgen05_tile(int M) { return M <= 32 ? 32 : M <= 64 ? 64 :
 // splits > 1 needs `partial`: splits * M * N floats of scratch owned by the caller.
 // status: device int; set to 4 if a block gave up waiting (the result is then not to be used).
 // swiglu: W holds (gate j, up j) in rows (2j, 2j + 1); Y is [M, N / 2] = silu(gate) * up.
-IK_EXPORT int ik_gemm_tcgen05(const void* X, const void* W, void* Y, int y_dtype, float* partial, int M, int N, int K,
-                              int ldx, int ldw, int ldy, int accumulate, int swiglu, int splits, int* status,
-                              cudaStream_t stream) {
-    if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || ldy < (swiglu ? N / 2 : N) || splits < 1) return IK_BAD_ARGUMENT;
+static int gemm_tcgen05_impl(const void* X, const void* W, void* Y, int y_dtype, float* partial, int M, int N, int K,
+                             int ldx, int ldw, int ldy, int accumulate, int swiglu, int splits, int* status,
+                             const IkRopeStore& rope, cudaStream_t stream) {
+    if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || (!rope.q_out && ldy < (swiglu ? N / 2 : N)) || splits < 1)
+        return IK_BAD_ARGUMENT;
     if (swiglu && ((N & 1) || accumulate)) return IK_BAD_ARGUMENT;
     if (y_dtype != IK_F32 && y_dtype != IK_BF16) return IK_BAD_ARGUMENT;
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return IK_UNSUPPORTED;
@@ -289,8 +357,8 @@ IK_EXPORT int ik_gemm_tcgen05(const void* X, const void* W, void* Y, int y_dtype
     st = ik_make_map(&mx, X, M, K, ldx, bn);
     if (st != IK_OK) return st;
 #define IK_TC(BN_)                                                                                                       \
-    return y_dtype == IK_F32 ? launch<BN_, float>(mw, mx, Y, partial, M, N, K, ldy, accumulate, swiglu, splits, status, stream) \
-                             : launch<BN_, bf16>(mw, mx, Y, partial, M, N, K, ldy, accumulate, swiglu, splits, status, stream)
+    return y_dtype == IK_F32 ? launch<BN_, float>(mw, mx, Y, partial, M, N, K, ldy, accumulate, swiglu, splits, status, rope, stream) \
+                             : launch<BN_, bf16>(mw, mx, Y, partial, M, N, K, ldy, accumulate, swiglu, splits, status, rope, stream)
     switch (bn) {
         case 32: IK_TC(32);
         case 64: IK_TC(64);
@@ -298,4 +366,18 @@ IK_EXPORT int ik_gemm_tcgen05(const void* X, const void* W, void* Y, int y_dtype
         default: IK_TC(256);
     }
 #undef IK_TC
+}
+
+IK_EXPORT int ik_gemm_tcgen05(const void* X, const void* W, void* Y, int y_dtype, float* partial, int M, int N, int K,
+                              int ldx, int ldw, int ldy, int accumulate, int swiglu, int splits, int* status,
+                              cudaStream_t stream) {
+    IkRopeStore none = {};
+    return gemm_tcgen05_impl(X, W, Y, y_dtype, partial, M, N, K, ldx, ldw, ldy, accumulate, swiglu, splits, status, none, stream);
+}
+
+// The fused q/k/v product with the rotary / cache epilogue (rope_store.cuh).  N must be (nh + 2 nkv) * hd, hd even.
+IK_EXPORT int ik_gemm_qkv_rope_tcgen05(const void* X, const void* W, float* partial, int M, int N, int K, int ldx, int ldw,
+                                       int splits, int* status, const IkRopeStore* rope, cudaStream_t stream) {
+    if (!rope || !rope->q_out || (rope->hd & 1) || N != (rope->nh + 2 * rope->nkv) * rope->hd) return IK_BAD_ARGUMENT;
+    return gemm_tcgen05_impl(X, W, nullptr, IK_F32, partial, M, N, K, ldx, ldw, N, 0, 0, splits, status, *rope, stream);
 }

@@ -75,6 +75,9 @@ _SIGNATURES = {
     "ik_gemm_bf16_mma": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "ik_gemm_tcgen05": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_gemm_tcgen05_tile": [_i],
+    "ik_rope_table": [_vp, _vp, _vp, _i, _i, _vp],
+    "ik_gemm_qkv_rope_mma": [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
+    "ik_gemm_qkv_rope_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
     "ik_attention_simt": [_vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp],
     "ik_argmax": [_vp, _i, _vp, _i, _i, _vp],
     "ik_sample": [_vp, _i, _vp, _vp, _i, _i, _f, _i, _f, _f, _vp, _i, _u64, _vp, _vp, _vp],
@@ -263,6 +266,63 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
         return None
     _check(st, "gemm_tcgen05", kernels=2 if splits > 1 else 1)
     return out
+
+
+class RopeStore(ctypes.Structure):
+    """Mirror of IkRopeStore (rope_store.cuh): where the fused q/k/v product puts its results."""
+    _fields_ = [("q_out", _vp), ("k_pages", _vp), ("v_pages", _vp), ("cos_sin", _vp), ("token_seq", _vp),
+                ("token_pos", _vp), ("table", _vp), ("status", _vp), ("table_stride", _i), ("nh", _i), ("nkv", _i),
+                ("hd", _i), ("page_size", _i), ("n_pages", _i), ("write_cache", _i)]
+
+
+def rope_table(token_pos: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """[T, half, 2] float: cos and sin of float(pos) * inv_freq, for the fused q/k/v epilogue."""
+    _need(token_pos, "token_pos", torch.int32)
+    _need(inv_freq, "inv_freq", torch.float32)
+    T, half = token_pos.numel(), inv_freq.numel()
+    out = torch.empty((T, half, 2), dtype=torch.float32, device=token_pos.device)
+    _check(lib().ik_rope_table(_ptr(token_pos), _ptr(inv_freq), _ptr(out), T, half, _stream()), "rope_table")
+    return out
+
+
+def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                  cos_sin: torch.Tensor, token_seq: torch.Tensor, token_pos: torch.Tensor, table: torch.Tensor,
+                  n_heads: int, n_kv_heads: int, head_dim: int, write_cache: bool, status: Optional[torch.Tensor],
+                  skinny_max: int = 16) -> bool:
+    """q, k, v = x W^T with rotary pairs in adjacent rows of W; rotated q to ``q_out``, rotated k and v into
+    the pages.  Returns False when the kernels do not take these sizes (the caller then runs the steps apart)."""
+    _need(x, "x", torch.bfloat16, contiguous=False)
+    _need(w, "w", torch.bfloat16, contiguous=False)
+    _need(q_out, "q_out", torch.bfloat16)
+    _need(k_pages, "k_pages", torch.bfloat16)
+    _need(v_pages, "v_pages", torch.bfloat16)
+    _need(cos_sin, "cos_sin", torch.float32)
+    _need(table, "table", torch.int32)
+    M, K = x.shape
+    N = w.shape[0]
+    n_pages, nkv, page_size, hd = k_pages.shape
+    if (N != (n_heads + 2 * n_kv_heads) * head_dim or nkv != n_kv_heads or hd != head_dim or head_dim % 2
+            or cos_sin.shape != (M, head_dim // 2, 2) or q_out.shape != (M, n_heads * head_dim)):
+        raise KernelError("gemm_qkv_rope: the sizes do not fit together")
+    if K % 8 or x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16 or x.stride(1) != 1 \
+            or w.stride(1) != 1:
+        return False
+    rs = RopeStore(_ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(cos_sin), _ptr(token_seq), _ptr(token_pos),
+                   _ptr(table), _ptr(status), table.stride(0), n_heads, n_kv_heads, head_dim, page_size, n_pages,
+                   1 if write_cache else 0)
+    if M <= skinny_max:
+        st = lib().ik_gemm_qkv_rope_mma(_ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), ctypes.byref(rs), _stream())
+        kernels = 1
+    else:
+        splits = tcgen05_splits(M, N, K)
+        partial = torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None
+        st = lib().ik_gemm_qkv_rope_tcgen05(_ptr(x), _ptr(w), _ptr(partial), M, N, K, x.stride(0), w.stride(0), splits,
+                                            _ptr(status), ctypes.byref(rs), _stream())
+        kernels = 2 if splits > 1 else 1
+    if st == -2:
+        return False
+    _check(st, "gemm_qkv_rope", kernels=kernels)
+    return True
 
 
 def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, token_seq: torch.Tensor,

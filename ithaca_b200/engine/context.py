@@ -34,6 +34,7 @@ class StepContext:
     host_slots: List[int] = field(default_factory=list)
     host_n_new: List[int] = field(default_factory=list)
     host_kv_lens: List[int] = field(default_factory=list)
+    shared: dict = field(default_factory=dict)     # what the layers of one step compute once and share (rotary tables)
 
 
 def field_offsets(sizes):

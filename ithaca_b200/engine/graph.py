@@ -253,6 +253,7 @@ class GraphDecoder:
         torch.cuda.current_stream().synchronize()
         st.model.forward(ctx, st.cache)                      # eager warm-up: writes this step's keys and values
         torch.cuda.current_stream().synchronize()
+        ctx.shared.clear()            # what the warm-up computed once per step has to be computed inside the graph too
         out = torch.empty(B + 1, dtype=torch.int32, device=st.runtime.device)
         graph = torch.cuda.CUDAGraph()
         n0 = ops.launch_count()

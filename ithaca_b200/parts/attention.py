@@ -52,7 +52,21 @@ class Attention:
         if position is not None and position.rotary_dim > self.head_dim:
             raise ValueError("attention: the rotated width exceeds the head size")
         w = spec.weights
-        self.qkv = Linear([tensors[w["q"]], tensors[w["k"]], tensors[w["v"]]], runtime)
+        wq, wk = tensors[w["q"]], tensors[w["k"]]
+        # bfloat16 path with the whole head rotated: the rows of the q and k weights are reordered so that the
+        # two members of a rotary pair are neighbours, (i, i + hd/2) -> (2i, 2i + 1).  Scores do not change (q and k
+        # are reordered alike, and the cache holds k in that order); the product's epilogue can then rotate a pair
+        # and write q and the cache entries itself, without the [tokens, q+k+v] intermediate.
+        self.pairing = position.pairing if position is not None else 0
+        self.fused_rope = (runtime.dtype == "bfloat16" and position is not None and position.rotary_dim == self.head_dim
+                           and self.head_dim % 2 == 0)
+        if self.fused_rope and self.pairing == 0:
+            half = self.head_dim // 2
+            order = torch.stack((torch.arange(half), torch.arange(half) + half), dim=1).reshape(-1)
+            wq = wq.view(self.n_heads, self.head_dim, -1)[:, order].reshape(wq.shape)
+            wk = wk.view(self.n_kv_heads, self.head_dim, -1)[:, order].reshape(wk.shape)
+            self.pairing = 1                                       # pairs are (2i, 2i + 1) from here on
+        self.qkv = Linear([wq, wk, tensors[w["v"]]], runtime)
         self.o = Linear([tensors[w["o"]]], runtime)
         self.runtime = runtime
 
@@ -63,14 +77,23 @@ class Attention:
                 writes_cache: bool = True) -> None:
         rt = self.runtime
         T = x.shape[0]
-        qkv = self.qkv(x, out_dtype=torch.float32)
         q = torch.empty((T, self.n_heads * self.head_dim), dtype=rt.act_dtype, device=x.device)
         table = ctx.tables[cache.kv_group]
         pos = self.position
-        ops.rope_append(qkv, q, cache.k_pages, cache.v_pages, ctx.token_seq, ctx.token_pos, table,
-                        pos.inv_freq if pos is not None else None, self.n_heads, self.n_kv_heads, self.head_dim,
-                        pos.rotary_dim if pos is not None else 0, pos.pairing if pos is not None else 0,
-                        writes_cache, rt.status)
+        done = False
+        if self.fused_rope:
+            key = pos.key
+            cos_sin = ctx.shared.get(key)
+            if cos_sin is None:                                   # once per step, shared by the layers
+                cos_sin = ctx.shared[key] = ops.rope_table(ctx.token_pos, pos.inv_freq)
+            done = ops.gemm_qkv_rope(x, self.qkv.weight, q, cache.k_pages, cache.v_pages, cos_sin, ctx.token_seq,
+                                     ctx.token_pos, table, self.n_heads, self.n_kv_heads, self.head_dim, writes_cache,
+                                     rt.status)
+        if not done:
+            qkv = self.qkv(x, out_dtype=torch.float32)
+            ops.rope_append(qkv, q, cache.k_pages, cache.v_pages, ctx.token_seq, ctx.token_pos, table,
+                            pos.inv_freq if pos is not None else None, self.n_heads, self.n_kv_heads, self.head_dim,
+                            pos.rotary_dim if pos is not None else 0, self.pairing, writes_cache, rt.status)
         att = attend(q, cache, ctx, table, self.n_heads, self.scale, self.window or 0, rt)
         self.o(att, out=residual, accumulate=True)
 

@@ -16,6 +16,7 @@ reference has both behind its ``neox`` flag (src/model.cpp:643).
 """
 from __future__ import annotations
 
+import json
 import math
 from typing import Dict, Mapping
 
@@ -59,6 +60,9 @@ def inverse_frequencies(rotary_dim: int, theta: float, scaling) -> np.ndarray:
     return freq.astype(np.float32)
 
 
+_TABLES: Dict[tuple, torch.Tensor] = {}      # one device copy per distinct table: layers with equal settings share it
+
+
 class RotaryPosition:
     @classmethod
     def manifest(cls, spec: PartSpec) -> Dict[str, TensorReq]:
@@ -70,8 +74,12 @@ class RotaryPosition:
         if pairing not in _PAIRINGS:
             raise ValueError(f"rotary: pairing {pairing!r} is not known (half, interleaved)")
         self.pairing = _PAIRINGS[pairing]
-        table = inverse_frequencies(self.rotary_dim, float(spec["theta"]), spec.get("scaling"))
-        self.inv_freq = torch.from_numpy(table).to(runtime.device)
+        scaling = spec.get("scaling")
+        self.key = ("rotary", self.rotary_dim, float(spec["theta"]), json.dumps(scaling, sort_keys=True), str(runtime.device))
+        if self.key not in _TABLES:
+            table = inverse_frequencies(self.rotary_dim, float(spec["theta"]), scaling)
+            _TABLES[self.key] = torch.from_numpy(table).to(runtime.device)
+        self.inv_freq = _TABLES[self.key]
 
 
 register_position("rotary", RotaryPosition)

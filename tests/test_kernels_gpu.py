@@ -243,6 +243,55 @@ def test_rope_append(nh, nkv, hd, rot, pairing, dtype):
     assert k_h.float().abs().sum(dim=(1, 3))[~touched].max().item() == 0
 
 
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 4, 16), (6, 2, 32), (5, 1, 48), (8, 2, 128)])
+@pytest.mark.parametrize("T_new", [[3, 5, 1], [40, 30, 66], [300, 2, 70]])
+def test_qkv_product_with_rotary_and_cache_epilogue(nh, nkv, hd, T_new):
+    """x W^T, rotated, with q to its buffer and k, v into the pages, from one kernel: every dispatch path
+    (skinny, tcgen05, tcgen05 with K slices) against the plain product followed by the plain rotation."""
+    d = 264
+    new = T_new
+    lens = [n + e for n, e in zip(new, (70, 0, 64))]
+    T = sum(new)
+    x = rnd((T, d), 50, torch.bfloat16)
+    wq, wk, wv = rnd((nh * hd, d), 51, torch.bfloat16, 0.2), rnd((nkv * hd, d), 52, torch.bfloat16, 0.2), rnd((nkv * hd, d), 53, torch.bfloat16, 0.2)
+    inv = P.rope_inv_freq(hd, 10000.0, None)
+    token_seq = np.repeat(np.arange(3), new).astype(np.int32)
+    token_pos = np.concatenate([np.arange(l - n, l) for l, n in zip(lens, new)]).astype(np.int32)
+    pos = torch.from_numpy(token_pos)
+    q_ref = P.rope((x.double() @ wq.double().T).view(T, nh, hd), pos, inv, "half")
+    k_ref = P.rope((x.double() @ wk.double().T).view(T, nkv, hd), pos, inv, "half")
+    v_ref = (x.double() @ wv.double().T).view(T, nkv, hd)
+    half = hd // 2
+    order = torch.stack((torch.arange(half), torch.arange(half) + half), dim=1).reshape(-1)     # (i, i+half) -> (2i, 2i+1)
+    w = torch.cat((wq.view(nh, hd, d)[:, order].reshape(nh * hd, d), wk.view(nkv, hd, d)[:, order].reshape(nkv * hd, d), wv)).to(DEV)
+    pg = Paged(lens, nkv, hd, torch.bfloat16, seed=3)
+    k_d, v_d, tab = pg.dev()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    cs = ops().rope_table(pos.to(DEV), inv.to(DEV))
+    ang = pos.float()[:, None] * inv[None, :]
+    close(cs[..., 0], torch.cos(ang.double()), 2e-6)
+    close(cs[..., 1], torch.sin(ang.double()), 2e-6)
+    q_out = torch.zeros((T, nh * hd), dtype=torch.bfloat16, device=DEV)
+    ok = ops().gemm_qkv_rope(x.to(DEV), w, q_out, k_d, v_d, cs, torch.from_numpy(token_seq).to(DEV), pos.to(DEV), tab,
+                             nh, nkv, hd, True, status)
+    assert ok and status.item() == 0
+    close(q_out.view(T, nh, hd), q_ref[:, :, order], 6e-3)
+    k_h, v_h = k_d.cpu(), v_d.cpu()
+    got_k = torch.stack([k_h[pg.table[s, p // 64], :, p % 64] for s, p in zip(token_seq, token_pos)])
+    got_v = torch.stack([v_h[pg.table[s, p // 64], :, p % 64] for s, p in zip(token_seq, token_pos)])
+    close(got_k, k_ref[:, :, order], 6e-3)
+    close(got_v, v_ref, 6e-3)
+    touched = torch.zeros(k_h.shape[0], 64, dtype=torch.bool)
+    for s, p in zip(token_seq, token_pos):
+        touched[pg.table[s, p // 64], p % 64] = True
+    assert k_h.float().abs().sum(dim=(1, 3))[~touched].max().item() == 0 and v_h.float().abs().sum(dim=(1, 3))[~touched].max().item() == 0
+    # without the right to write the cache only q appears
+    k2, v2 = torch.zeros_like(k_d), torch.zeros_like(v_d)
+    assert ops().gemm_qkv_rope(x.to(DEV), w, q_out, k2, v2, cs, torch.from_numpy(token_seq).to(DEV), pos.to(DEV), tab,
+                               nh, nkv, hd, False, status)
+    assert k2.abs().max().item() == 0 and v2.abs().max().item() == 0
+
+
 # ------------------------------------------------------------------------------------------ attention
 def attention_case(nh, nkv, hd, lens, new, window, dtype, seed, boost=None):
     """Random q/k/v for sequences of the given lengths, the last ``new[b]`` tokens of each being
