@@ -18,6 +18,16 @@
 // Tails in M, N and K are zero-filled by TMA and masked in the epilogue.  No multicast, no
 // clusters.
 //
+// How the work is shared out.  Data-parallel: the items (K slice, weight tile, token tile) are dealt round
+// robin; with K slices a second kernel adds the slices.  Stream-K: all (tile, K step) units are laid end to
+// end and every block takes an equal contiguous share, so that all SMs stream the same number of bytes
+// whatever the number of tiles.  A block whose share begins in the middle of a tile computes that piece
+// FIRST and hands the raw sums to the block that holds the tile's first K step (a scratch slot of its own,
+// then a flag); that block computes its own piece LAST, adds the others' pieces in ascending K order and
+// runs the epilogue.  A block thus only ever waits for blocks with a higher index that produced their piece
+// at the very start of their run, so the wait is short, cannot be circular, and the result does not depend on
+// timing.  The wait is bounded like the mbarrier waits.  Flags are cleared by their reader.
+//
 // Every wait on an mbarrier is bounded: after about a second without progress the waiting
 // thread sets the status word to IK_STATUS_GEMM_TIMEOUT, raises the block's abort flag and
 // every role leaves its loop; TMEM is freed and the block returns.  Blocks that start after
@@ -42,6 +52,72 @@ template <int BN> struct Cfg {
     static constexpr int SMEM = STAGES * STAGE + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
+constexpr int MAX_BLOCKS = 148;                                       // one persistent block per SM
+constexpr size_t IK_SK_PIECE_FLOATS = (size_t)MAX_BLOCKS * 256 * BM;  // stream-K scratch: a [256][128] piece per block ...
+constexpr size_t IK_SK_BYTES = IK_SK_PIECE_FLOATS * 4 + MAX_BLOCKS * 4 * 4;   // ... then a flag per block and epilogue warp
+
+// One accumulator's worth of work: K steps [kb0, kb0 + nkb) of output tile (nt, mt).
+struct Work {
+    int tile, mt, nt, z, kb0, nkb;
+    bool first, last;                 // holds the tile's first / last K step
+};
+
+// The sequence of Work of one block.  Every role of the block walks it on its own.
+struct Walk {
+    bool sk;
+    int tiles_m, tiles_n, nkb_total, kb_per_split;
+    int item, n_items;                // data-parallel: items blockIdx.x, + gridDim.x, ...; item -> (K slice, weight tile, token tile)
+    long long u, u_end, n_units;      // stream-K: this block's share [u, u_end) of all (tile, K step) units, token tile fastest
+    __device__ Walk(bool sk_, int tm, int tn, int nkb, int per, int n_splits)
+        : sk(sk_), tiles_m(tm), tiles_n(tn), nkb_total(nkb), kb_per_split(per), item(blockIdx.x), n_items(tm * tn * n_splits),
+          n_units((long long)tm * tn * nkb) {
+        u = share_begin(blockIdx.x);
+        u_end = share_begin(blockIdx.x + 1);
+    }
+    __device__ long long share_begin(int block) const { return n_units * block / gridDim.x; }
+    __device__ bool next(Work& w) {
+        if (sk) {
+            if (u >= u_end) return false;
+            w.tile = (int)(u / nkb_total);
+            w.kb0 = (int)(u - (long long)w.tile * nkb_total);
+            const long long left = u_end - u;
+            w.nkb = left < nkb_total - w.kb0 ? (int)left : nkb_total - w.kb0;
+            w.z = 0;
+            u += w.nkb;
+        } else {
+            if (item >= n_items) return false;
+            w.tile = item % (tiles_m * tiles_n);
+            w.z = item / (tiles_m * tiles_n);
+            w.kb0 = w.z * kb_per_split;
+            w.nkb = min(kb_per_split, nkb_total - w.kb0);
+            item += gridDim.x;
+        }
+        w.mt = w.tile % tiles_m;
+        w.nt = w.tile / tiles_m;
+        w.first = w.kb0 == 0;
+        w.last = w.kb0 + w.nkb == nkb_total;
+        return true;
+    }
+};
+
+// Waits until *flag is set by another block (acquire).  Bounded like mbar_wait.
+__device__ __forceinline__ bool flag_wait(const int* flag, volatile int* abort_flag, int* status) {
+    const unsigned long long t0 = globaltimer();
+    for (int spin = 0;; spin++) {
+        int v;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v) return true;
+        if ((spin & 63) == 63) {
+            if (*abort_flag) return false;
+            if (globaltimer() - t0 > 1000000000ull) {
+                *abort_flag = 1;
+                if (status) atomicExch(status, IK_STATUS_GEMM_TIMEOUT);
+                return false;
+            }
+        }
+    }
+}
+
 // map_w: [N rows, K] box {64, 128};  map_x: [M rows, K] box {64, BN}.
 // out: Y (float or bf16) when partial == nullptr, else partial sums [splits][M][N] float.
 //
@@ -54,7 +130,7 @@ template <int BN, typename TY>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     TY* __restrict__ Y, float* __restrict__ partial, int M, int N, int K, int ldy, int accumulate,
-                    int swiglu, int kb_per_split, int n_splits, int* status, const IkRopeStore rope) {
+                    int swiglu, int kb_per_split, int n_splits, int stream_k, int* status, const IkRopeStore rope) {
     typedef Cfg<BN> C;
     extern __shared__ unsigned char smem_raw[];
     __shared__ int rope_rows[4][BN];                   // per epilogue warp: the cache row of each of the tile's tokens
@@ -70,7 +146,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_n = (N + BM - 1) / BM, tiles_m = (M + BN - 1) / BN;
-    const int total_tiles = tiles_n * tiles_m * n_splits;
     const int nkb_total = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -92,19 +167,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const uint32_t tmem_base = *tmem_slot;
     ik_pdl_wait();
 
-    // tile t -> (K slice z, weight tile nt, token tile mt), token tile fastest
-    #define IK_TILE_COORDS(t)                                                   \
-        const int mt = (t) % tiles_m, nt = ((t) / tiles_m) % tiles_n, z = (t) / (tiles_m * tiles_n); \
-        const int n0 = nt * BM, m0 = mt * BN, kb0 = z * kb_per_split;           \
-        const int nkb = min(kb_per_split, nkb_total - kb0);
+    const Walk walk_init(stream_k != 0, tiles_m, tiles_n, nkb_total, kb_per_split, n_splits);
+    float* const slice_sums = stream_k ? nullptr : partial;           // data-parallel K slices: [slice][M][N]
+    float* const pieces = stream_k ? partial : nullptr;               // stream-K: [block][BN][128] raw sums of a piece
+    int* const piece_flags = stream_k ? reinterpret_cast<int*>(partial + IK_SK_PIECE_FLOATS) : nullptr;   // [block][4]
 
     if (warp == 0) {
         if (lane == 0) {
             int it = 0, armed = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                IK_TILE_COORDS(t)
-                (void)z;
+            Walk walk = walk_init;
+            for (Work w; ok && walk.next(w);) {
+                const int n0 = w.nt * BM, m0 = w.mt * BN, kb0 = w.kb0, nkb = w.nkb;
                 for (int i = 0; i < nkb; i++, it++) {
                     const int s = it % C::STAGES;
                     if (!mbar_wait(empty + s, ((it / C::STAGES) & 1) ^ 1, abort_flag, status)) { ok = false; break; }
@@ -128,9 +202,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const uint32_t idesc = umma_idesc(BN);
             int it = 0, lt = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, lt++) {
-                IK_TILE_COORDS(t)
-                (void)z; (void)n0; (void)m0; (void)kb0;
+            Walk walk = walk_init;
+            for (Work w; ok && walk.next(w); lt++) {
+                const int nkb = w.nkb;
                 const int buf = lt & 1;
                 ok = mbar_wait(acc_empty + buf, ((lt >> 1) & 1) ^ 1, abort_flag, status);   // drained by the epilogue
                 if (!ok) break;
@@ -153,12 +227,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     } else {
         // epilogue: warp w owns TMEM lanes 32 * (w % 4) .. + 31
         const int quarter = warp & 3;
-        const bool fused_rope = rope.q_out && !partial;
+        const bool fused_rope = rope.q_out && !slice_sums;
         int lt = 0;
-        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, lt++) {
-            IK_TILE_COORDS(t)
-            (void)kb0; (void)nkb;
+        Walk walk = walk_init;
+        for (Work w; walk.next(w); lt++) {
+            const int n0 = w.nt * BM, m0 = w.mt * BN, z = w.z;
             const int buf = lt & 1;
+            // stream-K: a piece that does not hold the tile's first K step is handed over raw; the piece that does
+            // hold it gathers the pieces of the blocks after this one, [c_lo, c_hi)
+            const bool hand_over = stream_k && !w.first;
+            int c_lo = 0, c_hi = 0;
+            if (stream_k && w.first && !w.last) {
+                const long long tile_end = (long long)(w.tile + 1) * nkb_total;
+                c_lo = c_hi = blockIdx.x + 1;
+                while (c_hi < (int)gridDim.x && walk.share_begin(c_hi) < tile_end) c_hi++;
+            }
             const int feature = n0 + quarter * 32 + lane;
             if (fused_rope) {
                 // each warp keeps its own list of the tile's cache rows (no barrier between warps is needed); the
@@ -167,9 +250,63 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 for (int i = lane; i < BN; i += 32) rope_rows[quarter][i] = ik_rope_cache_row(rope, m0 + i, M);
                 __syncwarp();
             }
+            const int row = quarter * 32 + lane;
+            // the other blocks' pieces of this tile: waited for first (they were computed at the very start of those
+            // blocks' runs), and the first two are fetched one 16-column chunk ahead of their use
+            bool gathered = true;
+            for (int c = c_lo; c < c_hi && gathered; c++) gathered = flag_wait(piece_flags + c * 4 + quarter, abort_flag, status);
+            if (!gathered) break;
+            float ahead[2][16];
+            auto fetch_piece = [&](int c, int c0, float (&p)[16]) {
+                const float* theirs = pieces + ((size_t)c * BN + c0) * BM + row;
+                #pragma unroll
+                for (int i = 0; i < 16; i++) p[i] = c < c_hi && m0 + c0 + i < M ? __ldcg(theirs + (size_t)i * BM) : 0.f;
+            };
+            if (c_hi > c_lo) {
+                fetch_piece(c_lo, 0, ahead[0]);
+                fetch_piece(c_lo + 1, 0, ahead[1]);
+            }
             if (!mbar_wait(acc_full + buf, (lt >> 1) & 1, abort_flag, status)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * C::ACC_COLS;
+            if (hand_over) {
+                float* mine = pieces + (size_t)blockIdx.x * BN * BM + row;
+                #pragma unroll 1
+                for (int c0 = 0; c0 < BN && m0 + c0 < M; c0 += 16) {
+                    float v[16];
+                    tmem_ld16(acc + c0, v);
+                    #pragma unroll
+                    for (int c = 0; c < 16; c++)
+                        if (m0 + c0 + c < M) mine[(size_t)(c0 + c) * BM] = v[c];
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(acc_empty + buf);
+                __threadfence();                         // this lane's sums are visible before the flag is
+                __syncwarp();
+                if (lane == 0)
+                    asm volatile("st.release.gpu.global.s32 [%0], %1;" :: "l"(piece_flags + blockIdx.x * 4 + quarter), "r"(1) : "memory");
+                continue;
+            }
+            // the accumulator's columns c0 .. c0 + 15 of this lane's row, with the other blocks' pieces added in K order
+            auto read_sums = [&](int c0, float (&v)[16]) {
+                tmem_ld16(acc + c0, v);
+                if (c_hi == c_lo) return;
+                float p[16], q[16];
+                #pragma unroll
+                for (int i = 0; i < 16; i++) { p[i] = ahead[0][i]; q[i] = ahead[1][i]; }
+                if (c0 + 16 < BN && m0 + c0 + 16 < M) {
+                    fetch_piece(c_lo, c0 + 16, ahead[0]);
+                    fetch_piece(c_lo + 1, c0 + 16, ahead[1]);
+                }
+                #pragma unroll
+                for (int i = 0; i < 16; i++) v[i] = (v[i] + p[i]) + q[i];
+                for (int c = c_lo + 2; c < c_hi; c += 2) {
+                    fetch_piece(c, c0, p);
+                    fetch_piece(c + 1, c0, q);
+                    #pragma unroll
+                    for (int i = 0; i < 16; i++) v[i] = (v[i] + p[i]) + q[i];
+                }
+            };
             // what the rotary epilogue needs of this lane's feature pair: fixed for the whole tile
             const int f0 = feature & ~1;
             const int head = fused_rope ? f0 / rope.hd : 0, r0 = fused_rope ? f0 - head * rope.hd : 0;
@@ -193,7 +330,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     for (int c = 0; c < 8; c++)
                         cs[c] = rotated && feature < N && m0 + col0 + c < M
                                     ? __ldg(cs_base + (size_t)(m0 + col0 + c) * (rope.hd >> 1)) : make_float2(1.f, 0.f);
-                    tmem_ld16(acc + c0, v);
+                    read_sums(c0, v);
                     __nv_bfloat162 packed[8];
                     #pragma unroll
                     for (int c = 0; c < 8; c++) {
@@ -218,12 +355,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     }
                     continue;
                 }
-                tmem_ld16(acc + c0, v);
-                if (feature < N || (swiglu && !partial)) {     // N is even under swiglu: a pair is in or out together
-                    if (partial) {
+                read_sums(c0, v);
+                if (feature < N || (swiglu && !slice_sums)) {     // N is even under swiglu: a pair is in or out together
+                    if (slice_sums) {
                         #pragma unroll
                         for (int c = 0; c < 16; c++)
-                            if (m0 + c0 + c < M) partial[((size_t)z * M + m0 + c0 + c) * N + feature] = v[c];
+                            if (m0 + c0 + c < M) slice_sums[((size_t)z * M + m0 + c0 + c) * N + feature] = v[c];
                     } else if (swiglu) {
                         // lanes (2j, 2j + 1) hold gate j and up j.  The pair shares the work: the even lane takes
                         // columns 0..7 (it gets the up values from its neighbour), the odd lane columns 8..15.
@@ -252,9 +389,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(acc_empty + buf);               // 128 arrivals: this accumulator may be overwritten
+            if (c_hi > c_lo) {                          // the pieces are used up: their flags go back to zero for the next launch
+                __syncwarp();
+                if (lane == 0)
+                    for (int c = c_lo; c < c_hi; c++) piece_flags[c * 4 + quarter] = 0;
+            }
         }
     }
-    #undef IK_TILE_COORDS
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
@@ -314,12 +455,20 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
     if (e != cudaSuccess) return (int)e;
     const int nkb = (K + BK - 1) / BK;
+    const long long tiles = (long long)((N + BM - 1) / BM) * ((M + BN - 1) / BN);
+    if (splits == 0) {                  // stream-K: equal shares of all (tile, K step) units, at least four K steps a block
+        const long long units = tiles * nkb;
+        const int blocks = (int)(units / 4 < 1 ? 1 : units / 4 < MAX_BLOCKS ? units / 4 : MAX_BLOCKS);
+        IK_RETURN_IF_ERROR(ik_launch(kern, blocks, THREADS, C::SMEM, stream, mw, mx, (TY*)Y, partial, M, N, K, ldy, accumulate,
+                                     swiglu, nkb, 1, 1, status, rope));
+        return (int)cudaGetLastError();
+    }
     const int per = (nkb + splits - 1) / splits;
     const int n_splits = (nkb + per - 1) / per;
-    const long long total = (long long)((N + BM - 1) / BM) * ((M + BN - 1) / BN) * n_splits;
-    const int blocks = (int)(total < 148 ? total : 148);
+    const long long total = tiles * n_splits;
+    const int blocks = (int)(total < MAX_BLOCKS ? total : MAX_BLOCKS);
     IK_RETURN_IF_ERROR(ik_launch(kern, blocks, THREADS, C::SMEM, stream, mw, mx, (TY*)Y, n_splits > 1 ? partial : nullptr, M,
-                                 N, K, ldy, accumulate, swiglu, per, n_splits, status, rope));
+                                 N, K, ldy, accumulate, swiglu, per, n_splits, 0, status, rope));
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (n_splits > 1) {
@@ -337,18 +486,22 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial
 // Token-tile width the kernel will use for M tokens.
 IK_EXPORT int ik_gemm_tcgen05_tile(int M) { return M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 
+// Scratch of the stream-K mode, in bytes: zeroed once by the caller, then left to the kernels (one stream at a time).
+IK_EXPORT int ik_gemm_tcgen05_stream_k_bytes() { return (int)IK_SK_BYTES; }
+
 // splits > 1 needs `partial`: splits * M * N floats of scratch owned by the caller.
+// splits == 0 is the stream-K mode; `partial` is then the scratch described above.
 // status: device int; set to 4 if a block gave up waiting (the result is then not to be used).
 // swiglu: W holds (gate j, up j) in rows (2j, 2j + 1); Y is [M, N / 2] = silu(gate) * up.
 static int gemm_tcgen05_impl(const void* X, const void* W, void* Y, int y_dtype, float* partial, int M, int N, int K,
                              int ldx, int ldw, int ldy, int accumulate, int swiglu, int splits, int* status,
                              const IkRopeStore& rope, cudaStream_t stream) {
-    if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || (!rope.q_out && ldy < (swiglu ? N / 2 : N)) || splits < 1)
+    if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || (!rope.q_out && ldy < (swiglu ? N / 2 : N)) || splits < 0)
         return IK_BAD_ARGUMENT;
     if (swiglu && ((N & 1) || accumulate)) return IK_BAD_ARGUMENT;
     if (y_dtype != IK_F32 && y_dtype != IK_BF16) return IK_BAD_ARGUMENT;
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return IK_UNSUPPORTED;
-    if (splits > 1 && !partial) return IK_BAD_ARGUMENT;
+    if (splits != 1 && !partial) return IK_BAD_ARGUMENT;
     if (M == 0) return IK_OK;
     const int bn = ik_gemm_tcgen05_tile(M);
     CUtensorMap mw, mx;

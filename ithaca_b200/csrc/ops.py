@@ -75,6 +75,7 @@ _SIGNATURES = {
     "ik_gemm_bf16_mma": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "ik_gemm_tcgen05": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_gemm_tcgen05_tile": [_i],
+    "ik_gemm_tcgen05_stream_k_bytes": [],
     "ik_rope_table": [_vp, _vp, _vp, _i, _i, _vp],
     "ik_gemm_qkv_rope_mma": [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_gemm_qkv_rope_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
@@ -226,13 +227,36 @@ def gemm_bf16_mma(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] 
 
 N_SM = 148
 
+_stream_k_scratch = {}
+
+
+def stream_k_scratch(device) -> torch.Tensor:
+    """Scratch of the stream-K product (pieces of tiles and their flags): one per device, zeroed once; the
+    kernels leave the flags zero.  Launches that use it must follow one another in one stream."""
+    key = str(torch.device(device))
+    t = _stream_k_scratch.get(key)
+    if t is None:
+        t = torch.zeros(lib().ik_gemm_tcgen05_stream_k_bytes() // 4, dtype=torch.float32, device=device)
+        _stream_k_scratch[key] = t
+    return t
+
+
 def tcgen05_splits(M: int, N: int, K: int) -> int:
-    """K slices for the tcgen05 product: as many as fill the SMs when the output has few tiles.
-    Each slice keeps at least four 64-wide K steps."""
-    tiles = -(-N // 128) * -(-M // lib().ik_gemm_tcgen05_tile(M))
-    if tiles >= N_SM:
-        return 1
-    return max(1, min(N_SM // tiles, -(-K // 64) // 4))
+    """How the tcgen05 product shares out its work: 1 = whole tiles dealt round robin; n > 1 = n slices
+    of K and a second kernel that adds them; 0 = stream-K (equal shares of all K steps of all tiles).
+    Measured on B200 with 4096 x 4096 .. 28672 x 4096 weights: with fewer tiles than half the SMs, K
+    slices win; stream-K wins when whole tiles would leave more than a tenth of the SMs' time unused
+    and there is one token tile of at most 128 tokens (bandwidth-bound); beyond that whole tiles win."""
+    tile_m = lib().ik_gemm_tcgen05_tile(M)
+    tiles_m = -(-M // tile_m)
+    tiles = -(-N // 128) * tiles_m
+    steps = -(-K // 64)
+    if 2 * tiles <= N_SM:
+        return max(1, min(N_SM // tiles, steps // 4))
+    rounds = -(-tiles // N_SM)
+    if tiles_m == 1 and tile_m <= 128 and tiles / (rounds * N_SM) < 0.9 and tiles * steps >= 8:
+        return 0
+    return 1
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=torch.float32,
@@ -258,7 +282,8 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
         raise KernelError("gemm: the output has the wrong shape")
     if splits is None:
         splits = tcgen05_splits(M, N, K)
-    partial = torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None
+    partial = (stream_k_scratch(x.device) if splits == 0 else
+               torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None)
     st = lib().ik_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(out), _code(out), _ptr(partial), M, N, K, x.stride(0),
                                w.stride(0), out.stride(0), 1 if accumulate else 0, 1 if swiglu else 0, splits, _ptr(status),
                                _stream())
@@ -315,7 +340,8 @@ def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages
         kernels = 1
     else:
         splits = tcgen05_splits(M, N, K)
-        partial = torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None
+        partial = (stream_k_scratch(x.device) if splits == 0 else
+                   torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None)
         st = lib().ik_gemm_qkv_rope_tcgen05(_ptr(x), _ptr(w), _ptr(partial), M, N, K, x.stride(0), w.stride(0), splits,
                                             _ptr(status), ctypes.byref(rs), _stream())
         kernels = 2 if splits > 1 else 1

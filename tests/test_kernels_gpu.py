@@ -112,7 +112,7 @@ def test_gemm_bf16_tiled_large(M, N, K):
 
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 200, 72), (17, 4096, 512), (33, 130, 328), (64, 384, 2048),
                                    (100, 96, 264), (200, 500, 1024), (300, 260, 72), (513, 257, 4096)])
-@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("splits", [1, 3, 0])          # whole tiles, K slices, stream-K
 @pytest.mark.parametrize("ydt", [torch.float32, torch.bfloat16])
 def test_gemm_tcgen05(M, N, K, splits, ydt):
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
@@ -128,6 +128,27 @@ def test_gemm_tcgen05(M, N, K, splits, ydt):
     close(got, ref + base.double(), 2e-5 if ydt == torch.float32 else 8e-3)
 
 
+def test_gemm_tcgen05_stream_k_back_to_back():
+    """Stream-K products of different shapes one after another share one scratch: every launch leaves the
+    flags as it found them, a tile cut into many pieces (one tile, K = 8192) sums them in K order, and the
+    result is the same bits every time."""
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    cases = [(129, 128, 8192), (64, 384, 2048), (40, 1000, 520), (129, 128, 8192), (300, 4096, 1024)]
+    data = [(rnd((M, K), 30 + i, torch.bfloat16).to(DEV), rnd((N, K), 40 + i, torch.bfloat16).to(DEV)) for i, (M, N, K) in enumerate(cases)]
+    first = {}
+    for rep in range(3):
+        for i, (x, w) in enumerate(data):
+            got = ops().gemm_tcgen05(x, w, splits=0, status=status)
+            if rep == 0:
+                close(got, x.double().cpu() @ w.double().cpu().T, 2e-5)
+                first[i] = got.clone()
+            else:
+                assert torch.equal(got, first[i])
+    assert status.item() == 0
+    flags = ops().stream_k_scratch(DEV)[-148 * 4:].view(torch.int32)
+    assert int(flags.abs().max().item()) == 0
+
+
 def test_gemm_tcgen05_strided_rows_and_default_splits():
     """Rows that are slices of wider matrices (row stride > K), and the split the dispatcher picks."""
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
@@ -135,7 +156,8 @@ def test_gemm_tcgen05_strided_rows_and_default_splits():
     x, w = xb[:, 128:640], wb[:, 512:1024]
     out = torch.zeros((40, 8192), device=DEV)
     got = ops().gemm_tcgen05(x, w, out=out[:, 4096:], status=status)
-    assert got is not None and status.item() == 0 and ops().tcgen05_splits(40, 4096, 512) > 1
+    assert got is not None and status.item() == 0 and ops().tcgen05_splits(40, 4096, 512) == 2      # K slices
+    assert ops().tcgen05_splits(40, 28672, 4096) == 0 and ops().tcgen05_splits(2048, 28672, 4096) == 1   # stream-K; whole tiles
     close(out[:, 4096:], x.double() @ w.double().T, 2e-5)
     assert out[:, :4096].abs().max().item() == 0
     assert ops().gemm_tcgen05(xb[:, 4:516], wb[:, :512], status=status) is None          # rows not 16-byte aligned
@@ -155,7 +177,7 @@ def test_gate_up_product_with_swiglu_epilogue(M, ff, d):
     close(got, ref, 6e-3)
     status = ops().device_status(DEV)
     if M > 16:
-        for splits in (1, 3):
+        for splits in (1, 3, 0):
             got = ops().gemm_tcgen05(x.to(DEV), wi, out_dtype=torch.float32, splits=min(splits, -(-d // 64)), status=status,
                                      swiglu=True)
             close(got, ref, 2e-5)
@@ -247,7 +269,7 @@ def test_rope_append(nh, nkv, hd, rot, pairing, dtype):
 @pytest.mark.parametrize("T_new", [[3, 5, 1], [40, 30, 66], [300, 2, 70]])
 def test_qkv_product_with_rotary_and_cache_epilogue(nh, nkv, hd, T_new):
     """x W^T, rotated, with q to its buffer and k, v into the pages, from one kernel: every dispatch path
-    (skinny, tcgen05, tcgen05 with K slices) against the plain product followed by the plain rotation."""
+    (skinny, tcgen05 with whole tiles and stream-K) against the plain product followed by the plain rotation."""
     d = 264
     new = T_new
     lens = [n + e for n, e in zip(new, (70, 0, 64))]
