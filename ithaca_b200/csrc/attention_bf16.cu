@@ -72,8 +72,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
                     bf16* __restrict__ out, const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,
                     const int* __restrict__ table, int table_stride, int nh, int nkv, float scale_log2e, int window,
                     int n_pages, int* status) {
-    ik_pdl_launch_dependents();
     ik_pdl_wait();
+    ik_pdl_launch_dependents();
     constexpr int BM = 16 * NW, THREADS = 32 * NW, CH = HD / 8;          // CH: 16-byte chunks per row
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = (bf16*)smem_raw;                      // [BM][LD]
@@ -255,8 +255,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const int* __restrict__ table, int table_stride, int nh, int nkv, float scale_log2e,
                        int window, int n_pages, int* status) {
     extern __shared__ __align__(1024) unsigned char tc_smem[];
-    ik_pdl_launch_dependents();
     ik_pdl_wait();
+    ik_pdl_launch_dependents();
     // late tiles see the most keys: they are started first, so that the short ones fill the tail
     const int b = blockIdx.z, h = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
     const int q_begin = cu_seqlens[b], n_new = cu_seqlens[b + 1] - q_begin;
@@ -489,7 +489,6 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
                    float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ kv_lens,
                    const int* __restrict__ table, int table_stride, int nh, int nkv, float scale_log2e, int window,
                    int n_pages, int chunk_pages, int n_splits, int* status) {
-    ik_pdl_launch_dependents();
     ik_pdl_wait();
     constexpr int CH = HD / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -621,6 +620,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
         cp_commit();
     }
     cp_wait<0>();
+    ik_pdl_launch_dependents();                                     // every key and value of this block has been read
     #pragma unroll
     for (int r = 0; r < 2; r++) {
         l_i[r] += __shfl_xor_sync(0xffffffffu, l_i[r], 1);
@@ -663,8 +663,8 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, const int* __restrict__ kv_lens, int nh, int window,
                                     int chunk_pages, int n_splits) {
-    ik_pdl_launch_dependents();
     ik_pdl_wait();
+    ik_pdl_launch_dependents();
     const int b = blockIdx.x, h = blockIdx.y;
     const int len = kv_lens[b], pos = len - 1;
     const int j0 = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;

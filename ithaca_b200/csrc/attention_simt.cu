@@ -22,8 +22,8 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pages, 
                       TO* __restrict__ out, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                       const int* __restrict__ table, int table_stride, int nh, int nkv, int hd, float scale,
                       int window, int page_size, int n_pages, int* status) {
-    ik_pdl_launch_dependents();
     ik_pdl_wait();
+    ik_pdl_launch_dependents();
     extern __shared__ __align__(16) unsigned char smem[];
     size_t* row = (size_t*)smem;              // [TILE] element offset of key j's row in the pages
     float* qs = (float*)(row + TILE);         // [hd]

@@ -83,15 +83,26 @@ __device__ __forceinline__ float ik_block_max(float v, float* scratch) {
 }
 
 // ------------------------------------------------------------------ programmatic dependent launch
-// Every kernel of this library may be launched before its predecessor in the stream has
-// finished: it announces at once that its own successor may be launched, does whatever does
-// not depend on earlier kernels (index arithmetic, barrier set-up, prefetching weights into
-// L2), and only then waits for the predecessor's results.  The wait returns when every earlier
-// kernel has completed and its writes are visible, so nothing after it can race; nothing
-// before it may touch memory that other kernels write.  The launch attribute is off unless
-// IK_PDL=<mask of kernel families> is in the environment (kernels then start strictly one after another and the
-// device-side calls are no-ops): on the decode step of the Llama-3.1-8B shape, replayed from a
-// CUDA graph, early launch measured no gain on B200.
+// A kernel launched with the attribute may start before its predecessor in the stream has finished.  The rules
+// every kernel of this library keeps:
+//   * ik_pdl_wait() returns when every earlier kernel has completed and its writes are visible.  Before it a
+//     kernel touches nothing that another kernel writes: only index arithmetic, barrier and TMEM set-up, and, in
+//     the bandwidth-bound products, the first batch of WEIGHTS, which no kernel writes.  So a product launched
+//     early has its first 128 KB per SM on the way while the kernel before it is still finishing.
+//   * ik_pdl_launch_dependents() comes AFTER the kernel's own wait (so at most two kernels are ever on the
+//     device: this one and the one after it) and as late as is useful: small kernels call it right after the
+//     wait (the product behind a norm starts at once and loads weights while the norm runs); the products and
+//     decode attention call it after their main loop (their successor takes the SM slots that their finishing
+//     blocks free, and does not compete with blocks that have not started yet).
+//   * what the kernel before has written is read with ordinary loads AFTER the wait.  A read-only load
+//     (__ldg, or a plain load through a `const __restrict__` pointer) is not enough: the compiler takes it for a
+//     read of constant memory and may move it to before the wait.  The skinny product, the one family that is
+//     launched early by default, reads its tokens with an explicit ld.global for that reason (with __ldg its
+//     results were wrong under graph replay).
+// IK_PDL=<mask of kernel families> chooses which launches get the attribute (0 = none: kernels start strictly
+// one after another and the device-side calls are no-ops).  Default: the skinny products only.  Measured on
+// the graph-replayed decode step of the 8B shape: skinny products 1.1 % faster, with the element-wise kernels
+// another 0.5 %, with decode attention 8 % slower (its blocks take SM slots while they wait for the queries).
 __device__ __forceinline__ void ik_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void ik_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 // Asks for `bytes` (a multiple of 16, 16-byte aligned) to be brought into L2.  Reads nothing into the SM.
@@ -111,7 +122,7 @@ __device__ __forceinline__ void ik_prefetch_l2(const void* p, uint32_t bytes) {
 
 static inline int ik_pdl_mask() {
     static int v = -1;
-    if (v < 0) { const char* e = getenv("IK_PDL"); v = e ? atoi(e) : 0; }
+    if (v < 0) { const char* e = getenv("IK_PDL"); v = e ? atoi(e) : IK_FAMILY_SKINNY; }
     return v;
 }
 

@@ -10,8 +10,8 @@
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ out,
                              int d, int V, float scale, int* status) {
-    ik_pdl_launch_dependents();
     ik_pdl_wait();
+    ik_pdl_launch_dependents();
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < V;
@@ -40,8 +40,8 @@ IK_EXPORT int ik_embed(const int* ids, const void* table, int table_dtype, float
 template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows_in,
                                const float* __restrict__ w, TO* __restrict__ out, int d, float eps) {
-    ik_pdl_launch_dependents();
     ik_pdl_wait();
+    ik_pdl_launch_dependents();
     __shared__ float red[32];
     const int r = blockIdx.x;
     const float* a = x + (size_t)(rows_in ? rows_in[r] : r) * d;
@@ -71,8 +71,8 @@ IK_EXPORT int ik_rmsnorm(const float* x, const int* rows_in, const float* w, voi
 // 2j and up j in column 2j + 1.  out[t, j] = silu(g) * u.
 template <typename TO>
 __global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out, int ff, size_t total, int interleaved) {
-    ik_pdl_launch_dependents();
     ik_pdl_wait();
+    ik_pdl_launch_dependents();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / ff;
         const int j = (int)(idx - t * ff);
@@ -115,8 +115,8 @@ rope_append_kernel(const float* __restrict__ qkv, TQ* __restrict__ q_out, TC* __
                    int hd, int rot, int pairing, int page_size, int n_pages, int write_cache, int heads_per_block,
                    int* status) {
     extern __shared__ __align__(16) float cs[];    // [rot/2] cos, then [rot/2] sin of this token's angles
-    ik_pdl_launch_dependents();
     ik_pdl_wait();
+    ik_pdl_launch_dependents();
     // threads: x runs over a head's elements, y over heads (no division in the loops)
     const int t = blockIdx.x, half = rot / 2, tid = threadIdx.y * blockDim.x + threadIdx.x;
     const int head_lo = blockIdx.y * heads_per_block;                          // over q heads, then k heads, then v heads
@@ -198,8 +198,8 @@ rope_append_kernel(const float* __restrict__ qkv, TQ* __restrict__ q_out, TC* __
 // q/k/v epilogue.
 __global__ void rope_table_kernel(const int* __restrict__ token_pos, const float* __restrict__ inv_freq,
                                   float* __restrict__ cos_sin, int T, int half) {
-    ik_pdl_launch_dependents();
     ik_pdl_wait();
+    ik_pdl_launch_dependents();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= T * half) return;
     const int t = idx / half, i = idx - t * half;

@@ -38,6 +38,14 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {      // read-once da
     return v;
 }
 
+// The tokens: written by the kernel before this one.  Not a read-only (ld.global.nc / __ldg) load: the compiler
+// may move such a load, which it takes for a read of constant memory, to before the wait for that kernel.
+__device__ __forceinline__ uint4 ld_tokens(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ void store_out(float* Y, size_t o, float v, int accumulate) {
     Y[o] = accumulate ? Y[o] + v : v;
 }
@@ -56,8 +64,6 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
                    int M, int N, int K, int ldx, int ldw, int ldy, int accumulate, int swiglu, const IkRopeStore rope) {
     constexpr int R = 16, COLS = 8 * NT;
     extern __shared__ float red[];                       // [8 warps][R][COLS]
-    ik_pdl_launch_dependents();
-    ik_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * R;
 
@@ -86,6 +92,9 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
 
     const uint4 zero = make_uint4(0, 0, 0, 0);
     const int nblk = (K + 63) / 64;                       // blocks of 64 k = two 32-k chunks, 128 bytes of a row
+    // Weights do not depend on the kernel before this one: a warp asks for its first batch of them, and only
+    // then waits for that kernel's results (the tokens).  Launched early, the wait hides this kernel's start-up.
+    bool waited = false;
     for (int blk0 = warp * U; blk0 < nblk; blk0 += 8 * U) {
         uint4 a[U][2][2], b[U][2][NT];
         #pragma unroll
@@ -96,8 +105,16 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
                 const bool kok = k < K;                   // K % 8 == 0: the whole 8 are inside
                 #pragma unroll
                 for (int h = 0; h < 2; h++) a[u][c][h] = (kok && wok[h]) ? ld_stream(wrow[h] + k) : zero;
+            }
+        if (!waited) { ik_pdl_wait(); waited = true; }
+        #pragma unroll
+        for (int u = 0; u < U; u++)
+            #pragma unroll
+            for (int c = 0; c < 2; c++) {
+                const int k = (blk0 + u) * 64 + c * 32 + t * 8;
+                const bool kok = k < K;
                 #pragma unroll
-                for (int n = 0; n < NT; n++) b[u][c][n] = (kok && xok[n]) ? __ldg((const uint4*)(xrow[n] + k)) : zero;
+                for (int n = 0; n < NT; n++) b[u][c][n] = (kok && xok[n]) ? ld_tokens(xrow[n] + k) : zero;
             }
         #pragma unroll
         for (int u = 0; u < U; u++)
@@ -109,6 +126,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
                     mma_bf16(acc[n], a[u][c][0].z, a[u][c][1].z, a[u][c][0].w, a[u][c][1].w, b[u][c][n].z, b[u][c][n].w);
                 }
     }
+    if (!waited) ik_pdl_wait();
+    ik_pdl_launch_dependents();                           // the kernel after this one may begin its own start-up
     // partial sums of the 8 warps, added in warp order
     float* mine = red + (size_t)warp * R * COLS;
     #pragma unroll
@@ -193,8 +212,8 @@ __global__ void __launch_bounds__(256)
 gemm_tiled_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, TY* __restrict__ Y,
                   int M, int N, int K, int ldx, int ldw, int ldy, int accumulate) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    ik_pdl_launch_dependents();
     ik_pdl_wait();
+    ik_pdl_launch_dependents();
     __nv_bfloat16* xs = (__nv_bfloat16*)smem_raw;                         // [STAGES][TBM][TBK]
     __nv_bfloat16* ws = xs + (size_t)STAGES * TBM * TBK;                  // [STAGES][TBN][TBK]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;

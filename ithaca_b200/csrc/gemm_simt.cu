@@ -16,8 +16,8 @@ template <typename TX, typename TW, typename TY>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TX* __restrict__ X, const TW* __restrict__ W, TY* __restrict__ Y, int M, int N, int K,
                  int ldx, int ldw, int ldy, int accumulate) {
-    ik_pdl_launch_dependents();
     ik_pdl_wait();
+    ik_pdl_launch_dependents();
     __shared__ float xs[BK][BM + 1];
     __shared__ float ws[BK][BN + 1];
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;

@@ -134,7 +134,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     typedef Cfg<BN> C;
     extern __shared__ unsigned char smem_raw[];
     __shared__ int rope_rows[4][BN];                   // per epilogue warp: the cache row of each of the tile's tokens
-    ik_pdl_launch_dependents();
     if (status && *(volatile int*)status == IK_STATUS_GEMM_TIMEOUT) return;     // an earlier block gave up
     unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = (uint64_t*)(tiles + C::STAGES * C::STAGE);
@@ -165,7 +164,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    ik_pdl_wait();
+    ik_pdl_wait();                                     // barriers and TMEM are set up while the kernel before finishes
+    ik_pdl_launch_dependents();
 
     const Walk walk_init(stream_k != 0, tiles_m, tiles_n, nkb_total, kb_per_split, n_splits);
     float* const slice_sums = stream_k ? nullptr : partial;           // data-parallel K slices: [slice][M][N]
@@ -408,8 +408,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 template <typename TY>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TY* __restrict__ Y, int M, int N, int ldy,
                                      int splits, int accumulate, int swiglu, const IkRopeStore rope) {
-    ik_pdl_launch_dependents();
     ik_pdl_wait();
+    ik_pdl_launch_dependents();
     const size_t total = (size_t)M * N;
     if (rope.q_out) {                   // columns (2j, 2j + 1) are rotary pairs: rotate and store to q_out and the cache
         const size_t half = (size_t)M * (N / 2);

@@ -83,8 +83,8 @@ __device__ Best block_argmax(const float* w, int V, Best* sh /* [32] */) {
 
 __global__ void __launch_bounds__(ST)
 argmax_kernel(const float* __restrict__ logits, int ldl, int* __restrict__ out, int V) {
-    ik_pdl_launch_dependents();
     ik_pdl_wait();
+    ik_pdl_launch_dependents();
     __shared__ Best sh[32];
     const Best b = block_argmax(logits + (size_t)blockIdx.x * ldl, V, sh);
     if (threadIdx.x == 0) out[blockIdx.x] = b.i;
@@ -100,8 +100,8 @@ __global__ void __launch_bounds__(ST)
 sample_kernel(const float* __restrict__ logits, int ldl, float* __restrict__ work, int* __restrict__ out, int V,
               float temperature, int top_k, float top_p, float rep_pen, const int* __restrict__ recent, int n_recent,
               uint64_t seed, const int* __restrict__ streams, const int* __restrict__ counters) {
-    ik_pdl_launch_dependents();
     ik_pdl_wait();
+    ik_pdl_launch_dependents();
     __shared__ Best shb[32];
     __shared__ float shf[32];
     __shared__ int shi[32];
