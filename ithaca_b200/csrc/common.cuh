@@ -122,7 +122,7 @@ __device__ __forceinline__ void ik_prefetch_l2(const void* p, uint32_t bytes) {
 
 static inline int ik_pdl_mask() {
     static int v = -1;
-    if (v < 0) { const char* e = getenv("IK_PDL"); v = e ? atoi(e) : IK_FAMILY_SKINNY; }
+    if (v < 0) { const char* e = getenv("IK_PDL"); v = e ? atoi(e) : (IK_FAMILY_SKINNY | IK_FAMILY_TCGEN05); }
     return v;
 }
 

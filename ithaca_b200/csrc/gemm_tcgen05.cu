@@ -164,10 +164,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    ik_pdl_wait();                                     // barriers and TMEM are set up while the kernel before finishes
+    const Walk walk_init(stream_k != 0, tiles_m, tiles_n, nkb_total, kb_per_split, n_splits);
+    // Weights are written by no kernel: the first stages' weight tiles are asked for before the wait for the kernel
+    // before this one (whose results are the tokens), so a product launched early has them on the way by then.
+    int pre_issued = 0;
+    if (threadIdx.x == 0) {
+        Walk walk = walk_init;
+        for (Work w; pre_issued < C::STAGES && walk.next(w);)
+            for (int i = 0; i < w.nkb && pre_issued < C::STAGES; i++, pre_issued++) {
+                mbar_expect_tx(full + pre_issued, C::STAGE);
+                tma_load_2d(tiles + pre_issued * C::STAGE, &map_w, (w.kb0 + i) * BK, w.nt * BM, full + pre_issued);
+            }
+    }
+    ik_pdl_wait();                                     // barriers, TMEM and the first weights are under way while the kernel before finishes
     ik_pdl_launch_dependents();
 
-    const Walk walk_init(stream_k != 0, tiles_m, tiles_n, nkb_total, kb_per_split, n_splits);
     float* const slice_sums = stream_k ? nullptr : partial;           // data-parallel K slices: [slice][M][N]
     float* const pieces = stream_k ? partial : nullptr;               // stream-K: [block][BN][128] raw sums of a piece
     int* const piece_flags = stream_k ? reinterpret_cast<int*>(partial + IK_SK_PIECE_FLOATS) : nullptr;   // [block][4]
@@ -181,10 +192,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const int n0 = w.nt * BM, m0 = w.mt * BN, kb0 = w.kb0, nkb = w.nkb;
                 for (int i = 0; i < nkb; i++, it++) {
                     const int s = it % C::STAGES;
-                    if (!mbar_wait(empty + s, ((it / C::STAGES) & 1) ^ 1, abort_flag, status)) { ok = false; break; }
                     unsigned char* a = tiles + s * C::STAGE;
-                    mbar_expect_tx(full + s, C::STAGE);
-                    tma_load_2d(a, &map_w, (kb0 + i) * BK, n0, full + s);
+                    if (it >= pre_issued) {             // the first stages are armed and their weights asked for already
+                        if (!mbar_wait(empty + s, ((it / C::STAGES) & 1) ^ 1, abort_flag, status)) { ok = false; break; }
+                        mbar_expect_tx(full + s, C::STAGE);
+                        tma_load_2d(a, &map_w, (kb0 + i) * BK, n0, full + s);
+                    }
                     tma_load_2d(a + C::A_BYTES, &map_x, (kb0 + i) * BK, m0, full + s);
                     armed = it + 1;
                 }
@@ -410,6 +423,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TY* __re
                                      int splits, int accumulate, int swiglu, const IkRopeStore rope) {
     ik_pdl_wait();
     ik_pdl_launch_dependents();
+    asm volatile("" : "+l"(partial));      // the slices are the kernel before's results: no read of them may move above the wait
     const size_t total = (size_t)M * N;
     if (rope.q_out) {                   // columns (2j, 2j + 1) are rotary pairs: rotate and store to q_out and the cache
         const size_t half = (size_t)M * (N / 2);
