@@ -163,7 +163,7 @@ def e2e_run(eng, batch, steps, vocab, context):
     return {"tok_s": batch * steps / st.decode_seconds, "h2d": eng._decoder.last_upload_bytes, "d2h": batch * 4 + 4}
 
 
-def prefill_run(eng, tokens, vocab, reps=3):
+def prefill_run(eng, tokens, vocab, reps=5):
     import numpy as np
     import torch
     rng = np.random.default_rng(5)
