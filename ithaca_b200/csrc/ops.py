@@ -202,7 +202,10 @@ def gemm_bf16_mma(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] 
                   accumulate: bool = False, kind: int = 0, swiglu: bool = False) -> Optional[torch.Tensor]:
     """bfloat16 operands, float accumulation on the warp-level tensor-core path.  ``kind``: 0 = by
     M, 1 = the skinny (decode) kernel, 2 = the tiled kernel.  Returns None when the kernels
-    do not take these sizes (K not a multiple of 8, unaligned rows)."""
+    do not take these sizes (K not a multiple of 8, unaligned rows).
+
+    ``w`` is a weight: the skinny kernel, launched early, reads its first rows before it waits for the
+    kernel before it in the stream, so ``w`` must not be what that kernel writes (``x`` and ``out`` may be)."""
     _need(x, "x", torch.bfloat16, contiguous=False)
     _need(w, "w", torch.bfloat16, contiguous=False)
     M, K = x.shape
@@ -263,7 +266,10 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
                  accumulate: bool = False, splits: Optional[int] = None,
                  status: Optional[torch.Tensor] = None, swiglu: bool = False) -> Optional[torch.Tensor]:
     """bfloat16 operands on the tcgen05 tensor cores (TMA-fed, accumulators in TMEM).  Returns None
-    when the kernel does not take these sizes (K not a multiple of 8, unaligned rows)."""
+    when the kernel does not take these sizes (K not a multiple of 8, unaligned rows).
+
+    ``w`` is a weight: launched early, the kernel asks for its first tiles of ``w`` before it waits for the
+    kernel before it in the stream, so ``w`` must not be what that kernel writes (``x`` and ``out`` may be)."""
     _need(x, "x", torch.bfloat16, contiguous=False)
     _need(w, "w", torch.bfloat16, contiguous=False)
     M, K = x.shape
