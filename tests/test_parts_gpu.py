@@ -307,3 +307,163 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     finally:
         MIXERS.unregister("toy_decay")
         unregister_architecture("ToyDecayLM")
+
+
+# ------------------------------------------------------------------------------------------ a toy routed feed-forward and a toy position encoding
+class ToySinusoid:
+    """A position encoding of the test's own: enc(pos)[2i] = sin(pos / base^(2i/d)), [2i+1] = cos(...), added to
+    a mixer's input by the mixer that asks for it.  No weights."""
+
+    @classmethod
+    def manifest(cls, spec):
+        return {}
+
+    def __init__(self, spec, tensors, runtime):
+        self.size, self.base = spec["size"], spec["base"]
+        i = torch.arange(0, self.size, 2, dtype=torch.float32, device=runtime.device)
+        self.inv = self.base ** (-i / self.size)
+
+    def encode(self, token_pos):
+        ang = token_pos.float()[:, None] * self.inv[None, :]
+        return torch.stack((torch.sin(ang), torch.cos(ang)), dim=-1).reshape(token_pos.numel(), self.size)
+
+
+class ToyPositionalMixer:
+    """y_t = W (x_t + enc(pos_t)): a mixer without memory that consumes the block's position part."""
+
+    @classmethod
+    def manifest(cls, spec):
+        from ithaca_b200.weights import TensorReq
+        return {spec.weights["w"]: TensorReq((spec["hidden_size"], spec["hidden_size"]))}
+
+    def __init__(self, spec, tensors, runtime, position=None):
+        self.w = tensors[spec.weights["w"]].to(runtime.device).float()
+        self.position = position
+
+    def cache_requests(self):
+        return []
+
+    def forward(self, x, ctx, cache, residual, writes_cache=True):
+        residual += (x.float() + self.position.encode(ctx.token_pos)) @ self.w.T
+
+
+class ToyRoutedFF:
+    """Top-1 routing over small experts: e = argmax(router x) (float32 logits, lowest index on ties),
+    y = softmax(router x)[e] * W2[e] relu(W1[e] x), added to the residual rows."""
+
+    @classmethod
+    def manifest(cls, spec):
+        from ithaca_b200.weights import TensorReq
+        d, f, E = spec["hidden_size"], spec["expert_size"], spec["n_experts"]
+        w = spec.weights
+        return {w["router"]: TensorReq((E, d)), w["w1"]: TensorReq((E * f, d)), w["w2"]: TensorReq((E * d, f))}
+
+    def __init__(self, spec, tensors, runtime):
+        self.d, self.f, self.E = spec["hidden_size"], spec["expert_size"], spec["n_experts"]
+        w = spec.weights
+        dev = runtime.device
+        self.router = tensors[w["router"]].to(dev).float()
+        self.w1 = tensors[w["w1"]].to(dev).float().view(self.E, self.f, self.d)
+        self.w2 = tensors[w["w2"]].to(dev).float().view(self.E, self.d, self.f)
+
+    def forward(self, x, ctx, residual):
+        x = x.float()
+        p = torch.softmax(x @ self.router.T, dim=-1)
+        e = torch.argmax(p, dim=-1)
+        h = torch.relu(torch.einsum("tfd,td->tf", self.w1[e], x))
+        residual += p.gather(1, e[:, None]) * torch.einsum("tdf,tf->td", self.w2[e], h)
+
+
+class ToyRoutedConfig:
+    def __init__(self, d):
+        self.d = d
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d)
+
+    def to_dict(self):
+        return dict(self.d)
+
+    def model_spec(self):
+        from ithaca_b200.config import BlockSpec, ModelSpec, PartSpec, default_schedule
+        d = self.d
+        h = d["hidden_size"]
+        layers = []
+        for i in range(d["num_hidden_layers"]):
+            p = f"layers.{i}"
+            layers.append(BlockSpec(
+                "prenorm", PartSpec("toy_positional", {"hidden_size": h}, {"w": f"{p}.mix.w"}),
+                PartSpec("toy_routed", {"hidden_size": h, "expert_size": d["expert_size"], "n_experts": d["n_experts"]},
+                         {"router": f"{p}.ff.router", "w1": f"{p}.ff.w1", "w2": f"{p}.ff.w2"}),
+                {"mixer": PartSpec("rmsnorm", {"size": h, "eps": 1e-5}, {"weight": f"{p}.n1"}),
+                 "feed_forward": PartSpec("rmsnorm", {"size": h, "eps": 1e-5}, {"weight": f"{p}.n2"})},
+                PartSpec("toy_sinusoid", {"size": h, "base": d["base"]})))
+        return ModelSpec("ToyRoutedLM", d["vocab_size"], h,
+                         PartSpec("embedding", {"vocab_size": d["vocab_size"], "hidden_size": h, "scale": 1.0}, {"weight": "emb"}),
+                         tuple(layers), default_schedule(len(layers)),
+                         PartSpec("rmsnorm", {"size": h, "eps": 1e-5}, {"weight": "norm"}),
+                         PartSpec("lm_head", {"vocab_size": d["vocab_size"], "hidden_size": h, "tied": False}, {"weight": "head"}),
+                         max_position=512)
+
+
+def toy_routed_plain(cfg, tensors, ids):
+    """The same model, whole sequence, float64, written out here."""
+    t = {k: v.double() for k, v in tensors.items()}
+    h, E, f = cfg["hidden_size"], cfg["n_experts"], cfg["expert_size"]
+    x = t["emb"][torch.tensor(ids)]
+    pos = torch.arange(len(ids), dtype=torch.float64)
+    i = torch.arange(0, h, 2, dtype=torch.float64)
+    ang = pos[:, None] * (cfg["base"] ** (-i / h)).float().double()[None, :]
+    enc = torch.stack((torch.sin(ang), torch.cos(ang)), dim=-1).reshape(len(ids), h)
+    for l in range(cfg["num_hidden_layers"]):
+        p = f"layers.{l}"
+        x = x + (P.rmsnorm(x, t[f"{p}.n1"], 1e-5) + enc) @ t[f"{p}.mix.w"].T
+        xn = P.rmsnorm(x, t[f"{p}.n2"], 1e-5)
+        pr = torch.softmax(xn @ t[f"{p}.ff.router"].T, dim=-1)
+        e = torch.argmax(pr, dim=-1)
+        w1, w2 = t[f"{p}.ff.w1"].view(E, f, h), t[f"{p}.ff.w2"].view(E, h, f)
+        hid = torch.relu(torch.einsum("tfd,td->tf", w1[e], xn))
+        x = x + pr.gather(1, e[:, None]) * torch.einsum("tdf,tf->td", w2[e], hid)
+    return (P.rmsnorm(x, t["norm"], 1e-5) @ t["head"].T).numpy()
+
+
+def test_a_toy_routed_feed_forward_and_position_encoding_are_registered_built_and_stepped(tmp_path):
+    """A feed-forward with routing and a position encoding, both defined here, in an architecture defined here:
+    registered, written as a random model folder, loaded, stepped whole and in pieces in a batch, against the same
+    model written out plainly.  No file of the framework changes."""
+    from ithaca_b200 import Engine, register_architecture, write_random_model
+    from ithaca_b200.config import unregister_architecture
+    from ithaca_b200.parts import FEED_FORWARDS, MIXERS, POSITIONS, register_feed_forward, register_mixer, register_position
+    from ithaca_b200.weights import read_model_tensors
+    register_mixer("toy_positional", ToyPositionalMixer)
+    register_feed_forward("toy_routed", ToyRoutedFF)
+    register_position("toy_sinusoid", ToySinusoid)
+    register_architecture("ToyRoutedLM", ToyRoutedConfig)
+    try:
+        cfg = {"architectures": ["ToyRoutedLM"], "hidden_size": 40, "num_hidden_layers": 2, "vocab_size": 77, "n_experts": 3,
+               "expert_size": 24, "base": 50.0, "torch_dtype": "float32"}
+        d = write_random_model(str(tmp_path / "toy_routed"), cfg, seed=4)
+        eng = Engine(d, dtype="float32", max_tokens=512)
+        assert len(eng.cache.kv_groups) == 0 and len(eng.cache.state_groups) == 0
+        tensors = read_model_tensors(d)
+        a, b = random_ids(30, 77, 5), random_ids(11, 77, 6)
+        ref_a, ref_b = toy_routed_plain(cfg, tensors, a), toy_routed_plain(cfg, tensors, b)
+        sa, sb = eng.alloc_slot(), eng.alloc_slot()
+        rows_a, rows_b = [], []
+        lg = eng.step([sa, sb], [a[:12], b[:4]], "all").cpu().numpy()
+        rows_a.append(lg[:12]); rows_b.append(lg[12:])
+        for t in range(7):
+            lg = eng.step([sa, sb], [[a[12 + t]], [b[4 + t]]], "last").cpu().numpy()
+            rows_a.append(lg[:1]); rows_b.append(lg[1:])
+        eng.free_slot(sb)
+        rows_a.append(eng.step([sa], [a[19:]], "all").cpu().numpy())
+        assert rel_err(np.concatenate(rows_a), ref_a) <= 2e-5
+        assert rel_err(np.concatenate(rows_b), ref_b) <= 2e-5
+        out = eng.generate([a[:5], b[:9]], max_tokens=3, temp=0.0, rep_pen=1.0, stop_token_ids=[])
+        assert [len(o) for o in out] == [3, 3]
+    finally:
+        MIXERS.unregister("toy_positional")
+        FEED_FORWARDS.unregister("toy_routed")
+        POSITIONS.unregister("toy_sinusoid")
+        unregister_architecture("ToyRoutedLM")
