@@ -100,6 +100,14 @@ struct Walk {
     }
 };
 
+// The rotary table can be the result of the kernel right before this one.  A volatile asm keeps its place after the
+// wait for that kernel; a read-only load (__ldg) is one the compiler may move.
+__device__ __forceinline__ float2 ld_cos_sin(const float2* p) {
+    float2 v;
+    asm volatile("ld.global.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p));
+    return v;
+}
+
 // Waits until *flag is set by another block (acquire).  Bounded like mbar_wait.
 __device__ __forceinline__ bool flag_wait(const int* flag, volatile int* abort_flag, int* status) {
     const unsigned long long t0 = globaltimer();
@@ -342,7 +350,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     #pragma unroll
                     for (int c = 0; c < 8; c++)
                         cs[c] = rotated && feature < N && m0 + col0 + c < M
-                                    ? __ldg(cs_base + (size_t)(m0 + col0 + c) * (rope.hd >> 1)) : make_float2(1.f, 0.f);
+                                    ? ld_cos_sin(cs_base + (size_t)(m0 + col0 + c) * (rope.hd >> 1)) : make_float2(1.f, 0.f);
                     read_sums(c0, v);
                     __nv_bfloat162 packed[8];
                     #pragma unroll
