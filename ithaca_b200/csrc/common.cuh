@@ -98,13 +98,18 @@ __device__ __forceinline__ float ik_block_max(float v, float* scratch) {
 //     (__ldg, or a plain load through a `const __restrict__` pointer) is not enough: the compiler takes it for a
 //     read of constant memory and may move it to before the wait.  The skinny product, the one family that is
 //     launched early by default, reads its tokens with an explicit ld.global for that reason (with __ldg its
-//     results were wrong under graph replay).
+//     results were wrong under graph replay); the element-wise kernels pass their input pointers through
+//     IK_AFTER_WAIT.
 // IK_PDL=<mask of kernel families> chooses which launches get the attribute (0 = none: kernels start strictly
-// one after another and the device-side calls are no-ops).  Default: the skinny products only.  Measured on
-// the graph-replayed decode step of the 8B shape: skinny products 1.1 % faster, with the element-wise kernels
-// another 0.5 %, with decode attention 8 % slower (its blocks take SM slots while they wait for the queries).
+// one after another and the device-side calls are no-ops).  Default: the products (skinny and tcgen05) and the
+// element-wise kernels.  Measured on the graph-replayed decode step of the 8B shape: skinny products 1.1 % faster,
+// with the element-wise kernels another 0.5 %, with decode attention 8 % slower (its blocks take SM slots while
+// they wait for the queries): attention and sampling stay off.
 __device__ __forceinline__ void ik_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void ik_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// After the wait: makes a pointer to what the kernel before wrote opaque to the compiler, so that no load through
+// it (not even a read-only one through `const __restrict__`) can be moved to before the wait.
+#define IK_AFTER_WAIT(ptr) asm volatile("" : "+l"(ptr))
 // Asks for `bytes` (a multiple of 16, 16-byte aligned) to be brought into L2.  Reads nothing into the SM.
 __device__ __forceinline__ void ik_prefetch_l2(const void* p, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(p), "r"(bytes) : "memory");
@@ -122,7 +127,7 @@ __device__ __forceinline__ void ik_prefetch_l2(const void* p, uint32_t bytes) {
 
 static inline int ik_pdl_mask() {
     static int v = -1;
-    if (v < 0) { const char* e = getenv("IK_PDL"); v = e ? atoi(e) : (IK_FAMILY_SKINNY | IK_FAMILY_TCGEN05); }
+    if (v < 0) { const char* e = getenv("IK_PDL"); v = e ? atoi(e) : (IK_FAMILY_ELEMENTWISE | IK_FAMILY_SKINNY | IK_FAMILY_TCGEN05); }
     return v;
 }
 

@@ -11,6 +11,7 @@ template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ out,
                              int d, int V, float scale, int* status) {
     ik_pdl_wait();
+    IK_AFTER_WAIT(ids);
     ik_pdl_launch_dependents();
     const int t = blockIdx.x;
     const int id = ids[t];
@@ -41,6 +42,8 @@ template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows_in,
                                const float* __restrict__ w, TO* __restrict__ out, int d, float eps) {
     ik_pdl_wait();
+    IK_AFTER_WAIT(x);
+    IK_AFTER_WAIT(rows_in);
     ik_pdl_launch_dependents();
     __shared__ float red[32];
     const int r = blockIdx.x;
@@ -72,6 +75,7 @@ IK_EXPORT int ik_rmsnorm(const float* x, const int* rows_in, const float* w, voi
 template <typename TO>
 __global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out, int ff, size_t total, int interleaved) {
     ik_pdl_wait();
+    IK_AFTER_WAIT(gu);
     ik_pdl_launch_dependents();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / ff;
@@ -116,6 +120,10 @@ rope_append_kernel(const float* __restrict__ qkv, TQ* __restrict__ q_out, TC* __
                    int* status) {
     extern __shared__ __align__(16) float cs[];    // [rot/2] cos, then [rot/2] sin of this token's angles
     ik_pdl_wait();
+    IK_AFTER_WAIT(qkv);
+    IK_AFTER_WAIT(token_seq);
+    IK_AFTER_WAIT(token_pos);
+    IK_AFTER_WAIT(table);
     ik_pdl_launch_dependents();
     // threads: x runs over a head's elements, y over heads (no division in the loops)
     const int t = blockIdx.x, half = rot / 2, tid = threadIdx.y * blockDim.x + threadIdx.x;
@@ -199,6 +207,7 @@ rope_append_kernel(const float* __restrict__ qkv, TQ* __restrict__ q_out, TC* __
 __global__ void rope_table_kernel(const int* __restrict__ token_pos, const float* __restrict__ inv_freq,
                                   float* __restrict__ cos_sin, int T, int half) {
     ik_pdl_wait();
+    IK_AFTER_WAIT(token_pos);
     ik_pdl_launch_dependents();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= T * half) return;

@@ -17,6 +17,7 @@ __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TX* __restrict__ X, const TW* __restrict__ W, TY* __restrict__ Y, int M, int N, int K,
                  int ldx, int ldw, int ldy, int accumulate) {
     ik_pdl_wait();
+    IK_AFTER_WAIT(X);                 // the tokens are the kernel before's results; this kernel takes no weight early
     ik_pdl_launch_dependents();
     __shared__ float xs[BK][BM + 1];
     __shared__ float ws[BK][BN + 1];
