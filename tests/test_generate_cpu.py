@@ -135,3 +135,11 @@ def test_decode_chunk_choice_is_sane():
                 pages = -(-length // 64)
                 c = decode_chunk_pages(n_seqs, heads, kv, length)
                 assert 1 <= c <= max(pages, 2), (n_seqs, heads, kv, length, c)
+
+
+def test_which_product_kernel_takes_which_shape():
+    from ithaca_b200.csrc.gemm_bf16 import takes_skinny
+    assert takes_skinny(1, 128256, 4096) and takes_skinny(8, 28672, 4096)           # up to 8 tokens: always
+    assert takes_skinny(12, 6144, 4096) and takes_skinny(16, 4096, 4096)            # small matrices up to 16 tokens
+    assert not takes_skinny(9, 28672, 4096) and not takes_skinny(16, 4096, 14336)   # large ones go to tcgen05
+    assert not takes_skinny(17, 64, 64)
