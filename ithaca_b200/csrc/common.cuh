@@ -110,10 +110,6 @@ __device__ __forceinline__ void ik_pdl_wait() { asm volatile("griddepcontrol.wai
 // After the wait: makes a pointer to what the kernel before wrote opaque to the compiler, so that no load through
 // it (not even a read-only one through `const __restrict__`) can be moved to before the wait.
 #define IK_AFTER_WAIT(ptr) asm volatile("" : "+l"(ptr))
-// Asks for `bytes` (a multiple of 16, 16-byte aligned) to be brought into L2.  Reads nothing into the SM.
-__device__ __forceinline__ void ik_prefetch_l2(const void* p, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(p), "r"(bytes) : "memory");
-}
 
 // Kernel families, for IK_PDL=<bit mask>: which launches get the attribute.
 #define IK_FAMILY_ELEMENTWISE 1
