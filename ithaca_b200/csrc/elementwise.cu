@@ -19,17 +19,32 @@ __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__
     if (!ok && threadIdx.x == 0 && status) atomicExch(status, 1);
     const TW* row = table + (size_t)(ok ? id : 0) * d;
     float* o = out + (size_t)t * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = ok ? ik_ld(row, i) * scale : 0.f;
+    // this block's slice of the row (a few tokens would otherwise keep a few SMs busy), four elements a thread
+    const int per = ((d + gridDim.y - 1) / gridDim.y + 3) & ~3, lo = blockIdx.y * per, hi = min(d, lo + per);
+    if ((d & 3) == 0 && ((uintptr_t)row % (4 * sizeof(TW))) == 0) {
+        for (int i = lo + 4 * threadIdx.x; i < hi; i += 4 * blockDim.x) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (ok) v = make_float4(ik_ld(row, i) * scale, ik_ld(row, i + 1) * scale, ik_ld(row, i + 2) * scale, ik_ld(row, i + 3) * scale);
+            *reinterpret_cast<float4*>(o + i) = v;
+        }
+    } else {
+        for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) o[i] = ok ? ik_ld(row, i) * scale : 0.f;
+    }
 }
 
 IK_EXPORT int ik_embed(const int* ids, const void* table, int table_dtype, float* out, int T, int d, int V,
                        float scale, int* status, cudaStream_t stream) {
     if (T < 0 || d <= 0 || V <= 0) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
+    // few tokens (decode): a row is cut into slices so that the grid has a block for most SMs
+    int slices = T >= 128 ? 1 : (128 + T - 1) / T;
+    while (slices > 1 && d / slices < 256) slices--;
+    if (T > 65535 * 32) return IK_BAD_ARGUMENT;
+    const dim3 grid(T, slices);
     if (table_dtype == IK_F32)
-        IK_RETURN_IF_ERROR(ik_launch(embed_kernel<float>, T, 256, 0, stream, ids, (const float*)table, out, d, V, scale, status));
+        IK_RETURN_IF_ERROR(ik_launch(embed_kernel<float>, grid, 256, 0, stream, ids, (const float*)table, out, d, V, scale, status));
     else if (table_dtype == IK_BF16)
-        IK_RETURN_IF_ERROR(ik_launch(embed_kernel<__nv_bfloat16>, T, 256, 0, stream, ids, (const __nv_bfloat16*)table, out, d, V, scale, status));
+        IK_RETURN_IF_ERROR(ik_launch(embed_kernel<__nv_bfloat16>, grid, 256, 0, stream, ids, (const __nv_bfloat16*)table, out, d, V, scale, status));
     else
         return IK_BAD_ARGUMENT;
     IK_LAUNCH_STATUS();

@@ -90,6 +90,48 @@ argmax_kernel(const float* __restrict__ logits, int ldl, int* __restrict__ out, 
     if (threadIdx.x == 0) out[blockIdx.x] = b.i;
 }
 
+// The same with a row cut into ARG_SPLITS slices, one block each (a handful of rows would otherwise keep a
+// handful of SMs busy).  A slice's block leaves its best in scratch; the block that arrives last merges the
+// slices in slice order (so the result does not depend on which block that is) and clears the row's counter.
+constexpr int ARG_SPLITS = 16, ARG_MAX_ROWS = 256;
+__device__ Best g_arg_part[ARG_MAX_ROWS * ARG_SPLITS];
+__device__ unsigned int g_arg_count[ARG_MAX_ROWS];
+
+__global__ void __launch_bounds__(ST)
+argmax_split_kernel(const float* __restrict__ logits, int ldl, int* __restrict__ out, int V) {
+    ik_pdl_wait();
+    ik_pdl_launch_dependents();
+    __shared__ Best sh[32];
+    __shared__ bool last;
+    const int row = blockIdx.y, split = blockIdx.x;
+    const int per = (V + ARG_SPLITS - 1) / ARG_SPLITS, lo = split * per, hi = min(V, lo + per);
+    const float* w = logits + (size_t)row * ldl;
+    Best b{-INFINITY, 0x7fffffff};
+    for (int i = lo + threadIdx.x; i < hi; i += ST) b = better(b, Best{w[i], i});
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best n{__shfl_xor_sync(0xffffffffu, b.v, o), __shfl_xor_sync(0xffffffffu, b.i, o)};
+        b = better(b, n);
+    }
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = b;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        Best r = sh[0];
+        for (int wv = 1; wv < ST / 32; wv++) r = better(r, sh[wv]);
+        g_arg_part[row * ARG_SPLITS + split] = r;
+        __threadfence();
+        last = atomicAdd(&g_arg_count[row], 1u) == ARG_SPLITS - 1;
+        if (last) {
+            __threadfence();
+            const volatile Best* parts = g_arg_part + row * ARG_SPLITS;       // written by other blocks: read from L2
+            Best all{parts[0].v, parts[0].i};
+            for (int sp = 1; sp < ARG_SPLITS; sp++) all = better(all, Best{parts[sp].v, parts[sp].i});
+            out[row] = all.i;
+            g_arg_count[row] = 0;
+        }
+    }
+}
+
 struct Keep {                 // which candidates survive top-k and top-p
     uint32_t tk; int need_k;  // key of the k-th largest; how many of the ties at tk are kept
     uint32_t tp; int need_p;  // key at the top-p boundary; how many of the ties at tp are kept
@@ -229,7 +271,10 @@ sample_kernel(const float* __restrict__ logits, int ldl, float* __restrict__ wor
 IK_EXPORT int ik_argmax(const float* logits, int ldl, int* out, int rows, int V, cudaStream_t stream) {
     if (rows < 0 || V <= 0 || ldl < V) return IK_BAD_ARGUMENT;
     if (rows == 0) return IK_OK;
-    IK_RETURN_IF_ERROR(ik_launch(argmax_kernel, rows, ST, 0, stream, logits, ldl, out, V));
+    if (rows <= ARG_MAX_ROWS && rows * ARG_SPLITS <= 1024 && V >= 16 * ST)
+        IK_RETURN_IF_ERROR(ik_launch(argmax_split_kernel, dim3(ARG_SPLITS, rows), ST, 0, stream, logits, ldl, out, V));
+    else
+        IK_RETURN_IF_ERROR(ik_launch(argmax_kernel, rows, ST, 0, stream, logits, ldl, out, V));
     IK_LAUNCH_STATUS();
 }
 

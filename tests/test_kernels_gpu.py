@@ -425,11 +425,17 @@ def test_attention_reaches_a_far_key_and_respects_the_window_edge(kind):
 
 
 # ------------------------------------------------------------------------------------------ sampling
-def test_argmax_takes_the_first_of_equal_maxima():
-    lg = rnd((5, 3001), 40)
-    lg[2, 77] = lg[2, 2500] = 9.0
-    got = ops().argmax(lg.to(DEV)).cpu()
-    assert got.tolist() == [int(torch.argmax(r)) for r in lg[:2]] + [77] + [int(torch.argmax(r)) for r in lg[3:]]
+@pytest.mark.parametrize("V", [3001, 16384, 50021])        # one block a row; rows cut into slices (vocabulary >= 16 Ki)
+def test_argmax_takes_the_first_of_equal_maxima(V):
+    lg = rnd((5, V), 40)
+    lg[2, 77] = lg[2, V - 501] = 9.0                         # equal maxima in different slices: the lower index wins
+    lg[4, V - 1] = 11.0                                      # the very last entry
+    want = [int(torch.argmax(r)) for r in lg[:2]] + [77, int(torch.argmax(lg[3])), V - 1]
+    for _ in range(3):                                       # the slices' counters are left clear for the next call
+        assert ops().argmax(lg.to(DEV)).cpu().tolist() == want
+    wide = torch.zeros((5, V + 13))                          # rows that are slices of wider rows
+    wide[:, :V] = lg
+    assert ops().argmax(wide.to(DEV)[:, :V]).cpu().tolist() == want
 
 
 @pytest.mark.parametrize("V", [256, 384, 5003])
