@@ -71,16 +71,63 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
     for (int i = threadIdx.x; i < d; i += 256) ik_st(o, i, a[i] * s * w[i]);
 }
 
+// The same for rows of up to 8192 elements, a multiple of 4: a thread keeps its up to 8 float4 of the row in
+// registers (one pass over the row), and asks for its part of the weight, which no kernel writes, before it waits
+// for the kernel that writes the row.
+constexpr int RMS_VEC = 8;
+template <typename TO>
+__global__ void __launch_bounds__(256)
+rmsnorm_row_in_registers_kernel(const float* __restrict__ x, const int* __restrict__ rows_in,
+                                const float* __restrict__ w, TO* __restrict__ out, int d, float eps) {
+    const int n4 = d >> 2;
+    float4 wv[RMS_VEC], xv[RMS_VEC];
+    #pragma unroll
+    for (int j = 0; j < RMS_VEC; j++) {
+        const int i = threadIdx.x + j * 256;
+        if (i < n4) wv[j] = __ldg(reinterpret_cast<const float4*>(w) + i);
+    }
+    ik_pdl_wait();
+    IK_AFTER_WAIT(x);
+    IK_AFTER_WAIT(rows_in);
+    ik_pdl_launch_dependents();
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const float4* a = reinterpret_cast<const float4*>(x + (size_t)(rows_in ? rows_in[r] : r) * d);
+    float ss = 0.f;
+    #pragma unroll
+    for (int j = 0; j < RMS_VEC; j++) {
+        const int i = threadIdx.x + j * 256;
+        xv[j] = i < n4 ? a[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    #pragma unroll
+    for (int j = 0; j < RMS_VEC; j++)
+        ss = fmaf(xv[j].x, xv[j].x, fmaf(xv[j].y, xv[j].y, fmaf(xv[j].z, xv[j].z, fmaf(xv[j].w, xv[j].w, ss))));
+    ss = ik_block_sum<256>(ss, red);
+    const float s = 1.0f / sqrtf(ss / (float)d + eps);
+    TO* o = out + (size_t)r * d;
+    #pragma unroll
+    for (int j = 0; j < RMS_VEC; j++) {
+        const int i = threadIdx.x + j * 256;
+        if (i < n4)
+            ik_st4(o, (size_t)4 * i, make_float4(xv[j].x * s * wv[j].x, xv[j].y * s * wv[j].y, xv[j].z * s * wv[j].z, xv[j].w * s * wv[j].w));
+    }
+}
+
 IK_EXPORT int ik_rmsnorm(const float* x, const int* rows_in, const float* w, void* out, int out_dtype, int rows,
                          int d, float eps, cudaStream_t stream) {
     if (rows < 0 || d <= 0) return IK_BAD_ARGUMENT;
     if (rows == 0) return IK_OK;
-    if (out_dtype == IK_F32)
+    if (out_dtype != IK_F32 && out_dtype != IK_BF16) return IK_BAD_ARGUMENT;
+    const bool in_registers = d % 4 == 0 && d <= 4 * 256 * RMS_VEC && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0 &&
+                              ((uintptr_t)out % 16) == 0;
+    if (in_registers && out_dtype == IK_F32)
+        IK_RETURN_IF_ERROR(ik_launch(rmsnorm_row_in_registers_kernel<float>, rows, 256, 0, stream, x, rows_in, w, (float*)out, d, eps));
+    else if (in_registers)
+        IK_RETURN_IF_ERROR(ik_launch(rmsnorm_row_in_registers_kernel<__nv_bfloat16>, rows, 256, 0, stream, x, rows_in, w, (__nv_bfloat16*)out, d, eps));
+    else if (out_dtype == IK_F32)
         IK_RETURN_IF_ERROR(ik_launch(rmsnorm_kernel<float>, rows, 256, 0, stream, x, rows_in, w, (float*)out, d, eps));
-    else if (out_dtype == IK_BF16)
-        IK_RETURN_IF_ERROR(ik_launch(rmsnorm_kernel<__nv_bfloat16>, rows, 256, 0, stream, x, rows_in, w, (__nv_bfloat16*)out, d, eps));
     else
-        return IK_BAD_ARGUMENT;
+        IK_RETURN_IF_ERROR(ik_launch(rmsnorm_kernel<__nv_bfloat16>, rows, 256, 0, stream, x, rows_in, w, (__nv_bfloat16*)out, d, eps));
     IK_LAUNCH_STATUS();
 }
 

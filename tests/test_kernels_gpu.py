@@ -45,7 +45,7 @@ def test_embed(table_dtype):
     assert status.item() == 1 and out[1].abs().max().item() == 0
 
 
-@pytest.mark.parametrize("d", [64, 200, 4096, 5000])
+@pytest.mark.parametrize("d", [64, 200, 202, 4096, 5000, 8192, 8196, 10000])     # rows kept in registers (<= 8192, % 4 == 0) and not
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_rmsnorm(d, out_dtype):
     x = rnd((7, d), 1, scale=3.0)
