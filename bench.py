@@ -252,6 +252,7 @@ def main():
         for b in point_batches:
             points[f"decode_b{b}"] = round(decode_run(eng, b, min(args.steps, 32), args.warmup, vocab, CONTEXT)["tok_s"], 1)
     e2e = e2e_run(eng, args.batch, args.steps, vocab, CONTEXT)
+    time.sleep(1.0)            # a measurement of its own: let the clocks settle after the generation run
     pre_ms = prefill_run(eng, PREFILL_TOKENS, vocab)
 
     layer_flops, head_flops = model_flops_per_token(cfg, n_layers)
