@@ -67,6 +67,7 @@ __device__ __forceinline__ Best better(Best a, Best b) {      // larger value, t
 
 __device__ Best block_argmax(const float* w, int V, Best* sh /* [32] */) {
     Best b{-INFINITY, 0x7fffffff};
+    #pragma unroll 8
     for (int i = threadIdx.x; i < V; i += ST) b = better(b, Best{w[i], i});
     #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -132,6 +133,148 @@ argmax_split_kernel(const float* __restrict__ logits, int ldl, int* __restrict__
     }
 }
 
+// ---- The usual case, k <= 1024 kept candidates (top_k = 40 by default): the k-th largest key is found four bits
+// at a time (8 counting passes over the row instead of 32), the k survivors are gathered into shared memory, and
+// top-p and the draw run on those alone, one candidate per thread, in vocabulary order.  The rule is the one
+// described at the top of this file; equal keys at the boundary are taken by ascending id.  Returns false, having
+// written nothing, when more than 1024 candidates tie with the k-th largest (the general path then runs).
+constexpr int CAND_CAP = 1024;
+
+__device__ bool sample_few(const float* w, int V, int k, float top_p, float inv_t, float mx, uint64_t seed, uint32_t stream,
+                           uint32_t counter, int* out, float* shf /* [32] */, int* shi /* [32] */) {
+    __shared__ int cnt_warp[32][16];
+    __shared__ int cnt_tot[16];
+    __shared__ int cand_i[CAND_CAP], tie_i[CAND_CAP], sort_i[CAND_CAP];
+    __shared__ float cand_v[CAND_CAP], sort_v[CAND_CAP], sort_w[CAND_CAP];
+    __shared__ int n_gt_sh, n_tie_sh, chosen, last_kept;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    // the key T of the k-th largest: digit by digit from the top; `need` of the candidates that share the prefix
+    // found so far are still to be taken
+    uint32_t prefix = 0;
+    int need = k;
+    for (int shift = 28; shift >= 0; shift -= 4) {
+        const uint32_t above = shift == 28 ? 0u : (0xFFFFFFFFu << (shift + 4));
+        int c[16];
+        #pragma unroll
+        for (int d = 0; d < 16; d++) c[d] = 0;
+        for (int base = tid; base < V; base += ST * 255) {          // 8-bit fields: flushed every 255 elements
+            unsigned long long lo8 = 0ull, hi8 = 0ull;
+            const int end = min(V, base + ST * 255);
+            for (int i0 = base; i0 < end; i0 += ST * 8) {           // eight loads under way per thread
+                float v8[8];
+                #pragma unroll
+                for (int j = 0; j < 8; j++) v8[j] = i0 + j * ST < end ? w[i0 + j * ST] : 0.f;
+                #pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const uint32_t key = okey(v8[j]);
+                    if (i0 + j * ST < end && (key & above) == prefix) {
+                        const uint32_t d = (key >> shift) & 15u;
+                        const unsigned long long one = 1ull << ((d & 7u) * 8u);
+                        if (d < 8u) lo8 += one; else hi8 += one;
+                    }
+                }
+            }
+            #pragma unroll
+            for (int d = 0; d < 8; d++) {
+                c[d] += (int)((lo8 >> (d * 8)) & 0xFFull);
+                c[d + 8] += (int)((hi8 >> (d * 8)) & 0xFFull);
+            }
+        }
+        #pragma unroll
+        for (int d = 0; d < 16; d++) {
+            #pragma unroll
+            for (int o = 16; o > 0; o >>= 1) c[d] += __shfl_xor_sync(0xffffffffu, c[d], o);
+        }
+        if (lane == 0) {
+            #pragma unroll
+            for (int d = 0; d < 16; d++) cnt_warp[warp][d] = c[d];
+        }
+        __syncthreads();
+        if (tid < 16) {
+            int t = 0;
+            for (int wv = 0; wv < ST / 32; wv++) t += cnt_warp[wv][tid];
+            cnt_tot[tid] = t;
+        }
+        __syncthreads();
+        int digit = 0;
+        for (int d = 15; d >= 0; d--) {
+            const int n = cnt_tot[d];
+            if (n >= need) { digit = d; break; }
+            need -= n;
+        }
+        prefix |= (uint32_t)digit << shift;
+        __syncthreads();                                   // cnt_tot is rewritten by the next pass
+    }
+    const uint32_t T = prefix;                              // `need` of the candidates with key == T are taken
+
+    // gather: everything above T, and the ties at T apart
+    if (tid == 0) { n_gt_sh = 0; n_tie_sh = 0; chosen = ST; last_kept = -1; }
+    __syncthreads();
+    #pragma unroll 8
+    for (int i = tid; i < V; i += ST) {
+        const float v = w[i];
+        const uint32_t key = okey(v);
+        if (key > T) {
+            const int slot = atomicAdd(&n_gt_sh, 1);
+            cand_i[slot] = i; cand_v[slot] = v;
+        } else if (key == T) {
+            const int slot = atomicAdd(&n_tie_sh, 1);
+            if (slot < CAND_CAP) tie_i[slot] = i;
+        }
+    }
+    __syncthreads();
+    const int n_gt = n_gt_sh, n_tie = n_tie_sh;
+    if (n_tie > CAND_CAP) return false;
+    // the `need` ties with the lowest ids join, in id order
+    if (tid < n_tie) {
+        const int me = tie_i[tid];
+        int rank = 0;
+        for (int j = 0; j < n_tie; j++) rank += tie_i[j] < me;
+        if (rank < need) { cand_i[n_gt + rank] = me; cand_v[n_gt + rank] = unkey(T); }
+    }
+    __syncthreads();
+    const int n = n_gt + need;                              // == k
+    // into vocabulary order (the gather above came in whatever order the atomics fell)
+    if (tid < n) {
+        const int me = cand_i[tid];
+        int pos = 0;
+        for (int j = 0; j < n; j++) pos += cand_i[j] < me;
+        sort_i[pos] = me; sort_v[pos] = cand_v[tid];
+    }
+    __syncthreads();
+    const float v = tid < n ? sort_v[tid] : 0.f;
+    const uint32_t key = okey(v);
+    const float wgt = tid < n ? expf((v - mx) * inv_t) : 0.f;
+    if (tid < n) sort_w[tid] = wgt;
+    float total;
+    block_scan_inclusive<float>(wgt, shf, &total);          // (syncs: sort_w is visible afterwards)
+    bool kept = tid < n;
+    if (top_p < 1.0f && kept) {
+        // the weight in front of this candidate in descending order (larger key, or equal key and lower id)
+        const float target = top_p * total;
+        float before = 0.f;
+        for (int j = 0; j < n; j++) {
+            const uint32_t kj = okey(sort_v[j]);
+            if (kj > key || (kj == key && j < tid)) before += sort_w[j];
+        }
+        kept = before < target;
+    }
+    const float mine = kept ? wgt : 0.f;
+    float kept_total;
+    const float incl = block_scan_inclusive<float>(mine, shf, &kept_total);
+    const float u = philox_uniform(seed, stream, counter);
+    const float r = fminf(u * kept_total, kept_total);
+    if (mine > 0.f) { atomicMax(&last_kept, tid); if (r <= incl) atomicMin(&chosen, tid); }
+    __syncthreads();
+    if (tid == 0) {
+        const int pick = chosen < ST ? chosen : last_kept;
+        *out = pick >= 0 ? sort_i[pick] : sort_i[0];
+    }
+    (void)shi;
+    return true;
+}
+
 struct Keep {                 // which candidates survive top-k and top-p
     uint32_t tk; int need_k;  // key of the k-th largest; how many of the ties at tk are kept
     uint32_t tp; int need_p;  // key at the top-p boundary; how many of the ties at tp are kept
@@ -153,6 +296,7 @@ sample_kernel(const float* __restrict__ logits, int ldl, float* __restrict__ wor
     const float* l = logits + (size_t)row * ldl;
     float* w = work + (size_t)row * V;
 
+    #pragma unroll 8
     for (int i = tid; i < V; i += ST) w[i] = l[i];
     __syncthreads();
     if (rep_pen != 1.0f && tid == 0) {
@@ -166,8 +310,11 @@ sample_kernel(const float* __restrict__ logits, int ldl, float* __restrict__ wor
     if (temperature <= 0.f) { if (tid == 0) out[row] = top.i; return; }
 
     const int k = min(V, max(1, top_k));
-    const int per = (V + ST - 1) / ST, lo = min(V, tid * per), hi = min(V, lo + per);
     const float inv_t = 1.0f / temperature, mx = top.v;
+    if (k <= CAND_CAP &&
+        sample_few(w, V, k, top_p, inv_t, mx, seed, (uint32_t)streams[row], (uint32_t)counters[row], out + row, shf, shi))
+        return;
+    const int per = (V + ST - 1) / ST, lo = min(V, tid * per), hi = min(V, lo + per);
     Keep kp{0u, V, 0u, V, false};
 
     // ---- top-k: the largest key T with count{key >= T} >= k
