@@ -149,11 +149,57 @@ __device__ bool sample_few(const float* w, int V, int k, float top_p, float inv_
     __shared__ int n_gt_sh, n_tie_sh, chosen, last_kept;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-    // the key T of the k-th largest: digit by digit from the top; `need` of the candidates that share the prefix
-    // found so far are still to be taken
+    // First try (two passes over the row): every thread's own largest key; the k-th largest of those 1024 keys is a
+    // lower bound of the k-th largest of the row, and with a few dozen candidates wanted out of a hundred thousand
+    // hardly more than k entries lie at or above it.  They are gathered and the k largest of them (lower id first
+    // among equals) picked exactly by counting.  If more than 1024 lie above the bound, the digit passes below run.
+    __shared__ uint32_t tmax[ST];
+    __shared__ uint32_t tau_sh;
+    __shared__ int n_above_sh;
+    bool gathered = false;
+    {
+        uint32_t mk = 0u;
+        #pragma unroll 8
+        for (int i = tid; i < V; i += ST) mk = max(mk, okey(w[i]));
+        tmax[tid] = mk;
+        if (tid == 0) n_above_sh = 0;
+        __syncthreads();
+        int rank = 0;
+        for (int j = 0; j < ST; j++) rank += tmax[j] > mk || (tmax[j] == mk && j < tid);
+        if (rank == k - 1) tau_sh = mk;                    // k <= 1024: exactly one thread
+        __syncthreads();
+        const uint32_t tau = tau_sh;
+        #pragma unroll 8
+        for (int i = tid; i < V; i += ST) {
+            const float v = w[i];
+            if (okey(v) >= tau) {
+                const int slot = atomicAdd(&n_above_sh, 1);
+                if (slot < CAND_CAP) { tie_i[slot] = i; sort_v[slot] = v; }       // (borrowed as scratch until the sort)
+            }
+        }
+        __syncthreads();
+        const int c = n_above_sh;
+        if (c <= CAND_CAP) {
+            if (tid < c) {
+                const uint32_t key = okey(sort_v[tid]);
+                const int me = tie_i[tid];
+                int r = 0;
+                for (int j = 0; j < c; j++) {
+                    const uint32_t kj = okey(sort_v[j]);
+                    r += kj > key || (kj == key && tie_i[j] < me);
+                }
+                if (r < k) { cand_i[r] = me; cand_v[r] = sort_v[tid]; }
+            }
+            gathered = true;
+        }
+        __syncthreads();
+    }
+
+    // Otherwise the key T of the k-th largest: digit by digit from the top; `need` of the candidates that share the
+    // prefix found so far are still to be taken
     uint32_t prefix = 0;
     int need = k;
-    for (int shift = 28; shift >= 0; shift -= 4) {
+    for (int shift = gathered ? -1 : 28; shift >= 0; shift -= 4) {
         const uint32_t above = shift == 28 ? 0u : (0xFFFFFFFFu << (shift + 4));
         int c[16];
         #pragma unroll
@@ -212,7 +258,7 @@ __device__ bool sample_few(const float* w, int V, int k, float top_p, float inv_
     if (tid == 0) { n_gt_sh = 0; n_tie_sh = 0; chosen = ST; last_kept = -1; }
     __syncthreads();
     #pragma unroll 8
-    for (int i = tid; i < V; i += ST) {
+    for (int i = gathered ? V : tid; i < V; i += ST) {
         const float v = w[i];
         const uint32_t key = okey(v);
         if (key > T) {
@@ -224,7 +270,8 @@ __device__ bool sample_few(const float* w, int V, int k, float top_p, float inv_
         }
     }
     __syncthreads();
-    const int n_gt = n_gt_sh, n_tie = n_tie_sh;
+    const int n_gt = gathered ? k : n_gt_sh, n_tie = gathered ? 0 : n_tie_sh;
+    if (gathered) need = 0;
     if (n_tie > CAND_CAP) return false;
     // the `need` ties with the lowest ids join, in id order
     if (tid < n_tie) {
