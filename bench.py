@@ -7,7 +7,7 @@ sequence's cache filled to the context length; a step is one decode step (forwar
 token per sequence plus the greedy pick), replayed from a CUDA graph and timed with CUDA events.
 ``e2e`` is the same through ``Engine.generate`` (host token ids in, host token ids out, one
 upload of the step's description and one read-back of the sampled ids per step).
-``prefill`` is one step of 2,048 prompt tokens.  ``roofline`` divides the bytes a decode step
+``prefill`` is one step of 2,048 prompt tokens (the median of five).  ``roofline`` divides the bytes a decode step
 has to read (every weight once, and the cache of the live sequences) by its time.
 Weights are random (seeded), token ids are seeded-uniform: no dataset, no checkpoint.
 """
@@ -167,7 +167,7 @@ def prefill_run(eng, tokens, vocab, reps=5):
     import numpy as np
     import torch
     rng = np.random.default_rng(5)
-    best = None
+    times = []
     for r in range(reps + 1):
         s = eng.alloc_slot()
         ids = rng.integers(0, vocab, size=tokens).tolist()
@@ -180,10 +180,9 @@ def prefill_run(eng, tokens, vocab, reps=5):
         torch.cuda.synchronize()
         eng.stepper.finish(ctx)
         eng.free_slot(s)
-        if r > 0:
-            ms = a.elapsed_time(b)
-            best = ms if best is None else min(best, ms)
-    return best
+        if r > 0:                                           # the first run is the warm-up
+            times.append(a.elapsed_time(b))
+    return sorted(times)[len(times) // 2]                   # the median
 
 
 def model_flops_per_token(cfg, n_layers):
