@@ -145,7 +145,12 @@ class LlamaConfig:
         eps = _need_float(d, "rms_norm_eps", 1e-5)
         if eps <= 0:
             raise ConfigError(f"config.json: rms_norm_eps must be > 0, found {eps}")
-        theta = _need_float(d, "rope_theta", 10000.0)
+        # newer model folders carry the rotary numbers in one object, "rope_parameters": the base beside the scaling rule
+        rope = d.get("rope_parameters")
+        if rope is not None and not isinstance(rope, dict):
+            raise ConfigError(f"config.json: 'rope_parameters' must be an object, found {rope!r}")
+        scaling = d.get("rope_scaling") if d.get("rope_scaling") is not None else rope
+        theta = _need_float(rope, "rope_theta", 10000.0) if rope and "rope_theta" in rope else _need_float(d, "rope_theta", 10000.0)
         if theta <= 0:
             raise ConfigError(f"config.json: rope_theta must be > 0, found {theta}")
         eos = d.get("eos_token_id")
@@ -167,7 +172,7 @@ class LlamaConfig:
             "architectures", "hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim", "hidden_act",
             "attention_bias", "mlp_bias", "partial_rotary_factor", "rms_norm_eps", "rope_theta", "eos_token_id",
             "sliding_window", "torch_dtype", "dtype", "vocab_size", "num_hidden_layers", "intermediate_size",
-            "rope_scaling", "max_position_embeddings", "tie_word_embeddings", "bos_token_id",
+            "rope_scaling", "rope_parameters", "max_position_embeddings", "tie_word_embeddings", "bos_token_id",
         }
         return cls(
             architecture=str(archs[0]),
@@ -180,7 +185,7 @@ class LlamaConfig:
             intermediate_size=_need_int(d, "intermediate_size"),
             rms_norm_eps=eps,
             rope_theta=theta,
-            rope_scaling=RopeScaling.from_dict(d.get("rope_scaling")),
+            rope_scaling=RopeScaling.from_dict(scaling),
             max_position_embeddings=_need_int(d, "max_position_embeddings", 4096),
             tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),
             sliding_window=window,

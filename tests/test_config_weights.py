@@ -32,6 +32,20 @@ def test_defaults_follow_the_reference():
     assert c.rope_theta == 10000.0 and c.max_position_embeddings == 4096 and not c.tie_word_embeddings
 
 
+def test_rotary_numbers_in_one_object_are_read_like_the_separate_keys():
+    d = dict(TINY_B)
+    separate = config_from_dict(d)[1]
+    scaling, theta = d.pop("rope_scaling"), d.pop("rope_theta")
+    d["rope_parameters"] = dict(scaling, rope_theta=theta)
+    together = config_from_dict(d)[1]
+    assert together.rope_theta == separate.rope_theta and together.rope_scaling == separate.rope_scaling
+    d["rope_parameters"] = {"rope_type": "default", "rope_theta": 1234.5}
+    plain = config_from_dict(d)[1]
+    assert plain.rope_theta == 1234.5 and plain.rope_scaling is None
+    with pytest.raises(ConfigError):
+        config_from_dict(dict(d, rope_parameters=[1, 2]))
+
+
 @pytest.mark.parametrize("patch,word", [
     ({"hidden_size": None}, "hidden_size"), ({"num_attention_heads": 5, "head_dim": None}, "multiple"),
     ({"num_key_value_heads": 3}, "num_key_value_heads"), ({"hidden_act": "gelu"}, "hidden_act"),
