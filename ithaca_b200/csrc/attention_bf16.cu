@@ -229,13 +229,18 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
 // The same attention on the fifth-generation tensor cores, for head sizes 64 and 128.
 // A block owns 128 query tokens of one head of one sequence (one TMEM lane per query) and walks
 // the sequence's pages, 64 keys at a time:
-//   warp 0      TMA: the query tile once, then each page's keys and values into a 3-stage ring.
+//   warp 0      TMA: the query tile once, then each page's keys and values into two rings of two stages.  A
+//               key stage is free as soon as its S = Q K^T has run, a value stage after its O += P V; the keys
+//               are asked for one page ahead of the values, so that neither load's latency shows.
 //   warp 1      tcgen05.mma: S = Q K^T into one of two 64-column score buffers in TMEM (the product for
 //               page i + 1 is issued before the softmax of page i is done), then O += P V with P read
-//               from shared memory and V as an N-contiguous operand straight from the page.
+//               from TMEM and V as an N-contiguous operand straight from the page.
 //   warps 2..5  softmax: each thread reads its query's 64 scores from TMEM, masks by position, keeps
-//               the running maximum and sum in float (base 2), rescales its row of O in TMEM when the
-//               maximum moved, writes P as bfloat16 into shared memory in the operand's swizzled layout.
+//               the running maximum and sum in float (base 2), and writes P as bfloat16 over the first 32
+//               columns of the score buffer it has just read.  P of page i and P of page i + 1 thus lie in
+//               different buffers, and the tensor core runs its products in the order they were issued, so the
+//               softmax of page i + 1 never waits for O += P V of page i; only the rare rescaling of its row of
+//               O (the maximum moved by more than a factor 256) does.
 // All mbarrier waits are bounded (tc_common.cuh); on a timeout the status word is set and the block
 // leaves its loops and frees its TMEM.
 #if IK_HD == 64 || IK_HD == 128
@@ -243,8 +248,7 @@ constexpr int TC_BM = 128, TC_NS = 2;                          // two blocks per
 constexpr int TC_BOXES = HD / 64;                              // 64-wide swizzled blocks along the head size
 constexpr int TC_Q_BYTES = TC_BM * HD * 2;
 constexpr int TC_KV_BYTES = PAGE * HD * 2;
-constexpr int TC_P_BYTES = TC_BM * PAGE * 2;
-constexpr int TC_SMEM = TC_Q_BYTES + TC_NS * 2 * TC_KV_BYTES + TC_P_BYTES + 256;   // no slack: see the alignment check
+constexpr int TC_SMEM = TC_Q_BYTES + TC_NS * 2 * TC_KV_BYTES + 256;   // no slack: see the alignment check
 constexpr int TC_TMEM_COLS = 256;                              // scores 2 x 64, output HD (<= 128)
 constexpr int TC_O_COL = 128;
 
@@ -279,12 +283,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     unsigned char* Qs = tc_smem;
     unsigned char* Ks = Qs + TC_Q_BYTES;                       // [TC_NS][TC_KV_BYTES]
     unsigned char* Vs = Ks + TC_NS * TC_KV_BYTES;
-    unsigned char* Ps = Vs + TC_NS * TC_KV_BYTES;
-    uint64_t* q_full = (uint64_t*)(Ps + TC_P_BYTES);
+    uint64_t* q_full = (uint64_t*)(Vs + TC_NS * TC_KV_BYTES);
     uint64_t* k_full = q_full + 1;                             // [TC_NS]
     uint64_t* v_full = k_full + TC_NS;
-    uint64_t* kv_free = v_full + TC_NS;
-    uint64_t* s_full = kv_free + TC_NS;                        // [2]
+    uint64_t* k_free = v_full + TC_NS;
+    uint64_t* v_free = k_free + TC_NS;
+    uint64_t* s_full = v_free + TC_NS;                         // [2]
     uint64_t* p_ready = s_full + 2;
     uint64_t* pv_done = p_ready + 1;
     uint32_t* tmem_slot = (uint32_t*)(pv_done + 1);
@@ -293,7 +297,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < TC_NS; s++) { mbar_init(k_full + s, 1); mbar_init(v_full + s, 1); mbar_init(kv_free + s, 1); }
+        for (int s = 0; s < TC_NS; s++) {
+            mbar_init(k_full + s, 1); mbar_init(v_full + s, 1); mbar_init(k_free + s, 1); mbar_init(v_free + s, 1);
+        }
         mbar_init(s_full, 1); mbar_init(s_full + 1, 1);
         mbar_init(p_ready, 128);
         mbar_init(pv_done, 1);
@@ -318,24 +324,35 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_expect_tx(q_full, TC_Q_BYTES);
             for (int bx = 0; bx < TC_BOXES; bx++)
                 tma_load_2d(Qs + bx * (TC_BM * 128), &map_q, h * HD + bx * 64, q_begin + row0, q_full);
-            for (int i = 0; i < n_iter; i++) {
-                const int s = i % TC_NS;
-                if (!mbar_wait(kv_free + s, ((i / TC_NS) & 1) ^ 1, abort_flag, status)) break;
+            auto page_row = [&](int i) -> int {
                 int page = table[(size_t)b * table_stride + p_lo + i];
                 if (page < 0 || page >= n_pages) { if (status) atomicExch(status, 3); page = 0; }
-                const int row = (page * nkv + kvh) * PAGE;
-                mbar_expect_tx(k_full + s, TC_KV_BYTES);
-                for (int bx = 0; bx < TC_BOXES; bx++)
-                    tma_load_2d(Ks + s * TC_KV_BYTES + bx * (PAGE * 128), &map_k, bx * 64, row, k_full + s);
-                mbar_expect_tx(v_full + s, TC_KV_BYTES);
-                for (int bx = 0; bx < TC_BOXES; bx++)
-                    tma_load_2d(Vs + s * TC_KV_BYTES + bx * (PAGE * 128), &map_v, bx * 64, row, v_full + s);
+                return (page * nkv + kvh) * PAGE;
+            };
+            // keys of page i, then values of page i - 1
+            for (int i = 0; i <= n_iter; i++) {
+                if (i < n_iter) {
+                    const int s = i % TC_NS;
+                    if (!mbar_wait(k_free + s, ((i / TC_NS) & 1) ^ 1, abort_flag, status)) break;
+                    const int row = page_row(i);
+                    mbar_expect_tx(k_full + s, TC_KV_BYTES);
+                    for (int bx = 0; bx < TC_BOXES; bx++)
+                        tma_load_2d(Ks + s * TC_KV_BYTES + bx * (PAGE * 128), &map_k, bx * 64, row, k_full + s);
+                }
+                if (i > 0) {
+                    const int s = (i - 1) % TC_NS;
+                    if (!mbar_wait(v_free + s, (((i - 1) / TC_NS) & 1) ^ 1, abort_flag, status)) break;
+                    const int row = page_row(i - 1);
+                    mbar_expect_tx(v_full + s, TC_KV_BYTES);
+                    for (int bx = 0; bx < TC_BOXES; bx++)
+                        tma_load_2d(Vs + s * TC_KV_BYTES + bx * (PAGE * 128), &map_v, bx * 64, row, v_full + s);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc_qk = umma_idesc(PAGE), idesc_pv = umma_idesc(HD, 1);
-            const uint32_t q_addr = smem_u32(Qs), p_addr = smem_u32(Ps);
+            const uint32_t q_addr = smem_u32(Qs);
             bool ok = mbar_wait(q_full, 0, abort_flag, status);
             auto issue_qk = [&](int i) -> bool {
                 const int s = i % TC_NS;
@@ -347,6 +364,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     umma(tmem + (i & 1) * PAGE, umma_desc(q_addr + (j / 4) * (TC_BM * 128) + (j % 4) * 32),
                          umma_desc(k_addr + (j / 4) * (PAGE * 128) + (j % 4) * 32), idesc_qk, j != 0);
                 umma_commit(s_full + (i & 1));
+                umma_commit(k_free + s);                   // the key stage is free once these products have read it
                 return true;
             };
             if (ok) ok = issue_qk(0);
@@ -359,9 +377,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 const uint32_t v_addr = smem_u32(Vs + s * TC_KV_BYTES);
                 #pragma unroll
                 for (int j = 0; j < PAGE / 16; j++)
-                    umma(tmem + TC_O_COL, umma_desc(p_addr + j * 32), umma_desc_mn(v_addr + j * 2048, PAGE * 128), idesc_pv,
-                         (i | j) != 0);
-                umma_commit(kv_free + s);
+                    umma_ts(tmem + TC_O_COL, tmem + (i & 1) * PAGE + j * 8, umma_desc_mn(v_addr + j * 2048, PAGE * 128),
+                            idesc_pv, (i | j) != 0);
+                umma_commit(v_free + s);
                 umma_commit(pv_done);
             }
         }
@@ -414,38 +432,42 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             #pragma unroll
             for (int c = 0; c < PAGE; c++) { sc[c] = ik_ex2(sc[c] - m_use); sum4[c & 3] += sc[c]; }
             l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-            if (i > 0) {
-                ok = mbar_wait(pv_done, (i - 1) & 1, abort_flag, status);         // O and the P buffer are free again
+            if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                // O is at rest between the product of the page before (waited for here) and this page's (which waits
+                // for this thread).  The barrier has completed i - 1 or i phases at this point, whatever was waited
+                // for earlier, so the parity names the right one.
+                ok = mbar_wait(pv_done, (i - 1) & 1, abort_flag, status);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (__any_sync(0xffffffffu, alpha != 1.f)) {
+                #pragma unroll
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    float v[32];
+                    tmem_ld16_issue(lane_base + TC_O_COL + c0, v);
+                    tmem_ld16_issue(lane_base + TC_O_COL + c0 + 16, v + 16);
+                    tmem_ld_wait();
                     #pragma unroll
-                    for (int c0 = 0; c0 < HD; c0 += 32) {
-                        float v[32];
-                        tmem_ld16_issue(lane_base + TC_O_COL + c0, v);
-                        tmem_ld16_issue(lane_base + TC_O_COL + c0 + 16, v + 16);
-                        tmem_ld_wait();
-                        #pragma unroll
-                        for (int c = 0; c < 32; c++) v[c] *= alpha;
-                        tmem_st16(lane_base + TC_O_COL + c0, *reinterpret_cast<float(*)[16]>(v));
-                        tmem_st16(lane_base + TC_O_COL + c0 + 16, *reinterpret_cast<float(*)[16]>(v + 16));
-                    }
-                    tmem_st_wait();
+                    for (int c = 0; c < 32; c++) v[c] *= alpha;
+                    tmem_st16(lane_base + TC_O_COL + c0, *reinterpret_cast<float(*)[16]>(v));
+                    tmem_st16(lane_base + TC_O_COL + c0 + 16, *reinterpret_cast<float(*)[16]>(v + 16));
                 }
             }
-            // this query's 64 probabilities, as a row of the swizzled K-major operand
-            unsigned char* prow = Ps + r * 128;
+            // this query's 64 probabilities, two per cell, over the scores they came from
             #pragma unroll
-            for (int c = 0; c < 8; c++) {
-                uint4 w;
-                w.x = pack_bf16(sc[c * 8 + 0], sc[c * 8 + 1]);
-                w.y = pack_bf16(sc[c * 8 + 2], sc[c * 8 + 3]);
-                w.z = pack_bf16(sc[c * 8 + 4], sc[c * 8 + 5]);
-                w.w = pack_bf16(sc[c * 8 + 6], sc[c * 8 + 7]);
-                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) * 16)) = w;
+            for (int c0 = 0; c0 < PAGE / 2; c0 += 16) {
+                uint32_t pk[16];
+                #pragma unroll
+                for (int c = 0; c < 16; c++) pk[c] = pack_bf16(sc[2 * (c0 + c)], sc[2 * (c0 + c) + 1]);
+                tmem_st16_bits(lane_base + (i & 1) * PAGE + c0, pk);
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");         // visible to the tensor core's reads
+            tmem_st_wait();
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            // p_ready counts arrivals, not threads: nobody arrives for page i before everybody has for page i - 1.
+            // (The scores of page i + 1 can be there before that, so a thread that is ahead would otherwise complete
+            // the phase of one that is behind, and the product would read probabilities not yet written.)
+            if (i > 0) {
+                ok = mbar_wait(p_ready, (i - 1) & 1, abort_flag, status);
+                if (!ok) break;
+            }
             mbar_arrive(p_ready);
         }
         if (ok && mbar_wait(pv_done, (n_iter - 1) & 1, abort_flag, status)) {
