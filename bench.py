@@ -7,7 +7,9 @@ sequence's cache filled to the context length; a step is one decode step (forwar
 token per sequence plus the greedy pick), replayed from a CUDA graph and timed with CUDA events.
 ``e2e`` is the same through ``Engine.generate`` (host token ids in, host token ids out, one
 upload of the step's description and one read-back of the sampled ids per step).
-``prefill`` is one step of 2,048 prompt tokens (the median of five).  ``roofline`` divides the bytes a decode step
+``prefill`` is one step of 2,048 prompt tokens (the median of five, each timed alone after a
+short pause and held against the burst peak; back to back the step takes about a tenth longer
+under the power cap).  ``roofline`` divides the bytes a decode step
 has to read (every weight once, and the cache of the live sequences) by its time.
 Weights are random (seeded), token ids are seeded-uniform: no dataset, no checkpoint.
 """
@@ -169,6 +171,7 @@ def prefill_run(eng, tokens, vocab, reps=5):
     rng = np.random.default_rng(5)
     times = []
     for r in range(reps + 1):
+        time.sleep(0.3)                                     # each run alone, as a prompt arrives: not in the power state the run before left
         s = eng.alloc_slot()
         ids = rng.integers(0, vocab, size=tokens).tolist()
         ctx = eng.stepper.prepare([s], [ids], "last")
@@ -251,7 +254,6 @@ def main():
         for b in point_batches:
             points[f"decode_b{b}"] = round(decode_run(eng, b, min(args.steps, 32), args.warmup, vocab, CONTEXT)["tok_s"], 1)
     e2e = e2e_run(eng, args.batch, args.steps, vocab, CONTEXT)
-    time.sleep(1.0)            # a measurement of its own: let the clocks settle after the generation run
     pre_ms = prefill_run(eng, PREFILL_TOKENS, vocab)
 
     layer_flops, head_flops = model_flops_per_token(cfg, n_layers)

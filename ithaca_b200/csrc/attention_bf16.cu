@@ -400,25 +400,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int c0 = 0; c0 < PAGE; c0 += 16) tmem_ld16_issue(lane_base + (i & 1) * PAGE + c0, sc + c0);
             tmem_ld_wait();
             const bool need_mask = (p * PAGE + PAGE - 1 > pos_lo) || (window > 0 && p * PAGE < pos_hi + 1 - window);
-            // four independent chains for the maximum (and below for the sum): one warp per scheduler has
-            // nothing else to hide the latency of a dependent chain behind
+            // Few instructions per score: the maximum is taken over the raw scores and scaled once (the scale is
+            // positive), and the scaling of a score is folded into the subtraction of the reference below.  Four
+            // independent chains for the maximum (and for the sum): a dependent chain's latency would show.  Rows
+            // past the sequence's end are only cut off where a mask is applied anyway (its last pages); before that
+            // they compute on whatever the query tile holds there, and are never stored.
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (need_mask) {
                 #pragma unroll
                 for (int c = 0; c < PAGE; c++) {
                     const int j = p * PAGE + c;
                     const bool in = row_valid && j <= pos_r && (window <= 0 || j > pos_r - window);
-                    sc[c] = in ? sc[c] * scale_log2e : -INFINITY;
+                    sc[c] = in ? sc[c] : -INFINITY;
                     mx4[c & 3] = fmaxf(mx4[c & 3], sc[c]);
                 }
             } else {
                 #pragma unroll
-                for (int c = 0; c < PAGE; c++) {
-                    sc[c] = row_valid ? sc[c] * scale_log2e : -INFINITY;
-                    mx4[c & 3] = fmaxf(mx4[c & 3], sc[c]);
-                }
+                for (int c = 0; c < PAGE; c += 2) mx4[(c >> 1) & 3] = max3(mx4[(c >> 1) & 3], sc[c], sc[c + 1]);
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2e;
             // m is the reference the exponentials are taken against.  It follows the running maximum only when
             // that has moved by more than 8 (a factor 256): until then the probabilities may exceed 1 by that
             // factor, which float sums and bfloat16 operands take in their stride, and O needs no rescaling.
@@ -430,7 +430,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const float m_use = m == -INFINITY ? 0.f : m;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             #pragma unroll
-            for (int c = 0; c < PAGE; c++) { sc[c] = ik_ex2(sc[c] - m_use); sum4[c & 3] += sc[c]; }
+            for (int c = 0; c < PAGE; c += 2) {            // two scores per multiply-add and per add
+                float a0, a1;
+                fma_f32x2(a0, a1, sc[c], sc[c + 1], scale_log2e, -m_use);
+                sc[c] = ik_ex2(a0);
+                sc[c + 1] = ik_ex2(a1);
+                add_f32x2(sum4[c & 2], sum4[(c & 2) + 1], sc[c], sc[c + 1]);
+            }
             l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
                 // O is at rest between the product of the page before (waited for here) and this page's (which waits
@@ -739,6 +745,7 @@ IK_EXPORT int ik_attn_prefill_tc(const void* q, const void* k_pages, const void*
     if (T <= 0 || B <= 0 || max_new <= 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size != PAGE || B > 65535 || nh > 65535)
         return IK_BAD_ARGUMENT;
     if (((uintptr_t)q % 16) || ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16)) return IK_UNSUPPORTED;
+    if (!(scale > 0.f)) return IK_UNSUPPORTED;             // the kernel takes the maximum of the raw scores
     CUtensorMap mq, mk, mv;
     int st = ik_make_map(&mq, q, (unsigned long long)T, nh * HD, (unsigned long long)nh * HD, TC_BM);
     if (st != IK_OK) return st;
