@@ -261,8 +261,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     extern __shared__ __align__(1024) unsigned char tc_smem[];
     ik_pdl_wait();
     ik_pdl_launch_dependents();
-    // late tiles see the most keys: they are started first, so that the short ones fill the tail
-    const int b = blockIdx.z, h = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
+    // Late tiles see the most keys: over the whole grid they are started first (blocks start in the order of their
+    // linear index), so that the short ones fill the tail; heads that share keys and values start side by side.
+    const int linear = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z), per_tile = gridDim.y * gridDim.z;
+    const int tile = gridDim.x - 1 - linear / per_tile, h = (linear % per_tile) % gridDim.y, b = (linear % per_tile) / gridDim.y;
     const int q_begin = cu_seqlens[b], n_new = cu_seqlens[b + 1] - q_begin;
     const int row0 = tile * TC_BM;
     if (row0 >= n_new) return;
