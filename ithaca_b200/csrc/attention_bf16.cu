@@ -478,6 +478,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             mbar_arrive(p_ready);
         }
+        // The last product.  Nothing above has waited for the one before it (it is known to have run only up to two
+        // pages back: the scores of the last page were there), and a parity names a phase only if the phase before
+        // it is over: so that one is waited for first.
+        if (ok && n_iter > 1) ok = mbar_wait(pv_done, (n_iter - 2) & 1, abort_flag, status);
         if (ok && mbar_wait(pv_done, (n_iter - 1) & 1, abort_flag, status)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = 1.0f / l;

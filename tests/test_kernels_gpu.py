@@ -372,6 +372,25 @@ def test_attention_bf16_prefill(nh, nkv, hd, kind, window):
     close(got, c["ref"], 8e-3)
 
 
+@pytest.mark.parametrize("hd,window", [(128, 40), (128, 8), (64, 40), (128, 0)])
+def test_attention_tcgen05_many_tiles_of_few_pages(hd, window):
+    """Hundreds of blocks that each see two to four pages (a narrow window), several per SM at a time: what one
+    block's roles hand to each other (rings, score buffers, the last product before the output is read) is
+    exercised at every block's start and end rather than in a long steady state.  Run a few times: a missing
+    wait shows only when the timing falls that way."""
+    from ithaca_b200.csrc import attention_bf16 as A
+    nh, nkv = 20, 5
+    lens, new = [1300, 2000, 130], [1300, 900, 130]
+    c = attention_case(nh, nkv, hd, lens, new, window or None, torch.bfloat16, seed=33)
+    k_d, v_d, tab = c["pg"].dev()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for _ in range(4):
+        got = A.prefill(c["q"], k_d, v_d, c["cu"], c["kv_lens"], tab, len(lens), max(new), nh, 1 / math.sqrt(hd), window,
+                        status, kind="tc")
+        assert status.item() == 0
+        close(got, c["ref"], 8e-3)
+
+
 @pytest.mark.parametrize("nh,nkv,hd", SHAPES)
 @pytest.mark.parametrize("window", [0, 40, 300])
 def test_attention_bf16_decode(nh, nkv, hd, window):
