@@ -248,7 +248,7 @@ constexpr int TC_BM = 128, TC_NS = 2;                          // two blocks per
 constexpr int TC_BOXES = HD / 64;                              // 64-wide swizzled blocks along the head size
 constexpr int TC_Q_BYTES = TC_BM * HD * 2;
 constexpr int TC_KV_BYTES = PAGE * HD * 2;
-constexpr int TC_SMEM = TC_Q_BYTES + TC_NS * 2 * TC_KV_BYTES + 256;   // no slack: see the alignment check
+constexpr int TC_SMEM = TC_Q_BYTES + TC_NS * 2 * TC_KV_BYTES + 256;   // no slack for alignment: see the check in the kernel
 constexpr int TC_TMEM_COLS = 256;                              // scores 2 x 64, output HD (<= 128)
 constexpr int TC_O_COL = 128;
 
