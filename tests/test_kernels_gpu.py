@@ -479,6 +479,36 @@ def test_sample_matches_plain(V, temp, top_k, top_p, pen):
         assert got == want
 
 
+@pytest.mark.parametrize("V", [50021, 128256])
+@pytest.mark.parametrize("shape", ["random", "ties", "flat", "peaked"])
+@pytest.mark.parametrize("temp,top_k,top_p,pen", [(0.8, 40, 0.9, 1.1), (1.0, 1000, 0.95, 1.3), (1.2, 3000, 0.8, 1.0)])
+def test_sample_at_large_vocabularies(V, shape, temp, top_k, top_p, pen):
+    """The kernel's short cuts for few kept candidates (a bound from the threads' own maxima; the k-th largest by
+    digits when too many lie above it) and the general path (more than 1,024 kept), on rows that look like
+    logits, on rows of few distinct values (thousands of equal entries at the cut), on a constant row and on a
+    row with one entry far above the rest."""
+    rows = 4
+    lg = rnd((rows, V), 43, scale=2.0)
+    if shape == "ties":
+        lg = (lg * 2).round() / 2
+    elif shape == "flat":
+        lg = torch.zeros_like(lg) + 0.25
+        lg[1, 77] = 0.5
+    elif shape == "peaked":
+        lg[:, 4321] += 30.0
+    recent = [[(7 * r + i * i) % V for i in range(r * 9)] for r in range(rows)]
+    rec = torch.full((rows, 64), -1, dtype=torch.int32)
+    for r, ids in enumerate(recent):
+        rec[r, :len(ids)] = torch.tensor(ids, dtype=torch.int32)
+    streams = torch.arange(rows, dtype=torch.int32) + 5
+    for counter in (3,):
+        counters = torch.full((rows,), counter, dtype=torch.int32)
+        got = ops().sample(lg.to(DEV), temp, top_k, top_p, pen, rec.to(DEV), 77, streams.to(DEV), counters.to(DEV)).cpu().tolist()
+        want = [P.sample(lg[r], temp, top_k, top_p, pen, recent[r], P.philox_uniform(77, int(streams[r]), counter))
+                for r in range(rows)]
+        assert got == want
+
+
 def test_sample_follows_the_distribution():
     """Many draws from one row: frequencies follow exp(l / temp) over the kept candidates."""
     V, n = 50, 4000
