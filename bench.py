@@ -1,6 +1,7 @@
 """Decode and prefill throughput of the Llama-3.1-8B shape on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl reference]
+    python bench.py --only decode|prefill|attention        one part alone (small cases for profiling)
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at the given batch with every
 sequence's cache filled to the context length; a step is one decode step (forward pass of one
@@ -188,6 +189,44 @@ def prefill_run(eng, tokens, vocab, reps=5):
     return sorted(times)[len(times) // 2]                   # the median
 
 
+def attention_run(cfg, reps):
+    """The prefill attention kernel alone, on one sequence in a shuffled paged cache: the whole prompt, a chunk
+    behind cached tokens, and one query tile per block in front of a long context with two blocks for every SM."""
+    import math
+    import torch
+    from ithaca_b200.csrc import attention_bf16 as A
+    dev = "cuda:0"
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    out = []
+    for name, heads, kv_heads, kv_len, n_new in [("prompt of 2048", nh, nkv, 2048, 2048), ("2048 behind 6144", nh, nkv, 8192, 2048),
+                                                 ("one tile behind 8064, 296 heads", 296, 74, 8192, 128)]:
+        g = torch.Generator(device=dev).manual_seed(3)
+        n_pages = kv_len // 64
+        k = torch.randn((n_pages, kv_heads, 64, hd), device=dev, generator=g).to(torch.bfloat16)
+        v = torch.randn((n_pages, kv_heads, 64, hd), device=dev, generator=g).to(torch.bfloat16)
+        table = torch.randperm(n_pages, device=dev, generator=g).to(torch.int32).view(1, -1)
+        q = torch.randn((n_new, heads * hd), device=dev, generator=g).to(torch.bfloat16)
+        cu = torch.tensor([0, n_new], dtype=torch.int32, device=dev)
+        lens = torch.tensor([kv_len], dtype=torch.int32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        res = torch.empty_like(q)
+        run = lambda: A.prefill(q, k, v, cu, lens, table, 1, n_new, heads, 1 / math.sqrt(hd), 0, status, out=res)
+        for _ in range(2):
+            run()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            run()
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) / reps * 1e3
+        pairs = sum(min(kv_len - n_new + i + 1, kv_len) for i in range(n_new))          # (query, key) pairs under the causal mask
+        out.append({"case": name, "us": round(us, 1), "tflops": round(4 * hd * heads * pairs / us / 1e6, 1),
+                    "status": int(status.item())})
+    return out
+
+
 def model_flops_per_token(cfg, n_layers):
     d, ff, nh, nkv, hd, V = (cfg["hidden_size"], cfg["intermediate_size"], cfg["num_attention_heads"],
                              cfg["num_key_value_heads"], cfg["head_dim"], cfg["vocab_size"])
@@ -206,7 +245,7 @@ def main():
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES),
                     help="layer sizes: 8b is the benchmark's configuration, the others are for comparison")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention"],
                     help="run one part only and print its figures (for profiling a small case)")
     args = ap.parse_args()
 
@@ -226,6 +265,9 @@ def main():
     pk = peaks()
     shape_name, shape_cfg = SHAPES[args.shape]
     cfg = dict(shape_cfg)
+    if args.only == "attention":
+        print(json.dumps({"only": "attention", "model": shape_name, "cases": attention_run(cfg, reps=max(1, min(args.steps, 5)))}))
+        return 0
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
