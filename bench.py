@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the Llama-3.1-8B shape on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl reference]
-    python bench.py --only decode|prefill|attention        one part alone (small cases for profiling)
+    python bench.py --only decode|prefill|attention|products   one part alone (small cases for profiling)
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at the given batch with every
 sequence's cache filled to the context length; a step is one decode step (forward pass of one
@@ -189,6 +189,43 @@ def prefill_run(eng, tokens, vocab, reps=5):
     return sorted(times)[len(times) // 2]                   # the median
 
 
+def products_run(cfg, tokens, reps):
+    """A layer's four matrix products alone at ``tokens`` tokens, this library's tcgen05 kernel beside cuBLAS
+    (torch.matmul) on the same operands; the weights are rotated through copies larger than L2 together."""
+    import torch
+    from ithaca_b200.csrc import ops
+    dev = "cuda:0"
+    d, ff = cfg["hidden_size"], cfg["intermediate_size"]
+    qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = []
+    for name, n, k in [("qkv", qkv, d), ("o", d, cfg["num_attention_heads"] * cfg["head_dim"]), ("gate_up", 2 * ff, d), ("down", d, ff)]:
+        copies = max(2, min(8, int(300e6 // (n * k * 2)) + 1))
+        ws = [torch.randn((n, k), device=dev).to(torch.bfloat16) for _ in range(copies)]
+        x = torch.randn((tokens, k), device=dev).to(torch.bfloat16)
+        y = torch.empty((tokens, n), device=dev, dtype=torch.float32)
+        yb = torch.empty((tokens, n), device=dev, dtype=torch.bfloat16)
+        row = {"product": name, "rows": n, "k": k}
+        for label, fn in [("ours_us", lambda i: ops.gemm_tcgen05(x, ws[i % copies], out=y, status=status)),
+                          ("cublas_us", lambda i: torch.matmul(x, ws[i % copies].T, out=yb))]:
+            for i in range(3):
+                fn(i)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for i in range(reps * copies):
+                fn(i)
+            b.record()
+            torch.cuda.synchronize()
+            row[label] = round(a.elapsed_time(b) / (reps * copies) * 1e3, 1)
+        row["ours_tflops"] = round(2 * tokens * n * k / row["ours_us"] / 1e6, 1)
+        row["cublas_tflops"] = round(2 * tokens * n * k / row["cublas_us"] / 1e6, 1)
+        out.append(row)
+        del ws
+    out.append({"status": int(status.item())})
+    return out
+
+
 def attention_run(cfg, reps):
     """The prefill attention kernel alone, on one sequence in a shuffled paged cache: the whole prompt, a chunk
     behind cached tokens, and one query tile per block in front of a long context with two blocks for every SM."""
@@ -245,7 +282,7 @@ def main():
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES),
                     help="layer sizes: 8b is the benchmark's configuration, the others are for comparison")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention", "products"],
                     help="run one part only and print its figures (for profiling a small case)")
     args = ap.parse_args()
 
@@ -265,6 +302,10 @@ def main():
     pk = peaks()
     shape_name, shape_cfg = SHAPES[args.shape]
     cfg = dict(shape_cfg)
+    if args.only == "products":
+        print(json.dumps({"only": "products", "model": shape_name, "tokens": PREFILL_TOKENS,
+                          "cases": products_run(cfg, PREFILL_TOKENS, reps=max(1, min(args.steps, 5)))}))
+        return 0
     if args.only == "attention":
         print(json.dumps({"only": "attention", "model": shape_name, "cases": attention_run(cfg, reps=max(1, min(args.steps, 5)))}))
         return 0
