@@ -150,10 +150,14 @@ class SequenceCache:
         return int(self.table.length[slot])
 
     def truncate(self, slot: int, n: int) -> None:
-        if self.state_groups and n != 0:
+        """Keeps the first ``n`` positions of the slot.  Fixed-size state cannot be rolled back: a
+        sequence that has some goes back to 0 only, and its state is cleared then (the reference
+        restarts a recurrent model from zero when it is rewound, src/model.cpp:1047-1055)."""
+        if self.state_groups and n not in (0, self.length(slot)):
             raise CacheError("a sequence with fixed-size state can only be truncated to 0")
+        shorter = n < self.length(slot)
         self.table.truncate(slot, n)
-        if n == 0:
+        if n == 0 and shorter:
             for t in self.state:
                 t[:, slot].zero_()
 

@@ -201,10 +201,21 @@ class SlotTable:
     def truncate(self, slot: int, n: int) -> None:
         """Keeps the first ``n`` positions (the reference's ``rewind``, src/model.cpp:1047-1058).
         Pages past them are kept for reuse by the same slot.  A windowed group cannot go
-        back behind pages it has already released."""
+        back behind pages it has already released, except to 0: then the slot gives all its
+        pages back and starts again.  On refusal nothing has changed."""
         self._check_slot(slot)
         if not 0 <= n <= self.length[slot]:
             raise CacheError(f"slot {slot}: cannot truncate to {n}, it holds {int(self.length[slot])}")
+        if n == 0 and any(self._first_live[g][slot] > 0 for g in range(len(self.kv_groups))):
+            for g, pool in enumerate(self.pools):
+                row = self.tables[g][slot]
+                for i in np.nonzero(row >= 0)[0]:
+                    pool.give_back(int(row[i]))
+                row[:] = -1
+                self._first_live[g][slot] = 0
+            self.length[slot] = 0
+            self._reserved[slot] = 0
+            return
         for g, grp in enumerate(self.kv_groups):
             if grp.window is not None and n < self.length[slot]:
                 first_needed = max(0, n + 1 - grp.window)

@@ -11,38 +11,11 @@ count (src/model.cpp:64-67), ``head_dim`` to hidden/heads (:71),
 from __future__ import annotations
 
 import json
-import os
 from dataclasses import dataclass, field
 from typing import Any, Dict, Optional, Tuple
 
+from .base import ConfigError, need_float as _need_float, need_int as _need_int, token_id_list
 from .spec import BlockSpec, ModelSpec, PartSpec, default_schedule
-
-
-class ConfigError(ValueError):
-    pass
-
-
-def _need_int(d: Dict[str, Any], key: str, default: Optional[int] = None, minimum: int = 1) -> int:
-    v = d.get(key, default)
-    if v is None:
-        raise ConfigError(f"config.json: required key '{key}' is missing")
-    if isinstance(v, bool) or not isinstance(v, int):
-        if isinstance(v, float) and v == int(v):
-            v = int(v)
-        else:
-            raise ConfigError(f"config.json: '{key}' must be an integer, found {v!r}")
-    if v < minimum:
-        raise ConfigError(f"config.json: '{key}' must be >= {minimum}, found {v}")
-    return v
-
-
-def _need_float(d: Dict[str, Any], key: str, default: Optional[float] = None) -> float:
-    v = d.get(key, default)
-    if v is None:
-        raise ConfigError(f"config.json: required key '{key}' is missing")
-    if isinstance(v, bool) or not isinstance(v, (int, float)):
-        raise ConfigError(f"config.json: '{key}' must be a number, found {v!r}")
-    return float(v)
 
 
 @dataclass(frozen=True)
@@ -153,25 +126,22 @@ class LlamaConfig:
         theta = _need_float(rope, "rope_theta", 10000.0) if rope and "rope_theta" in rope else _need_float(d, "rope_theta", 10000.0)
         if theta <= 0:
             raise ConfigError(f"config.json: rope_theta must be > 0, found {theta}")
-        eos = d.get("eos_token_id")
-        if eos is None:
-            eos_ids: Tuple[int, ...] = ()
-        elif isinstance(eos, int) and not isinstance(eos, bool):
-            eos_ids = (eos,)
-        elif isinstance(eos, list) and all(isinstance(e, int) and not isinstance(e, bool) for e in eos):
-            eos_ids = tuple(eos)
-        else:
-            raise ConfigError(f"config.json: eos_token_id must be an integer or a list of integers, found {eos!r}")
-        window = d.get("sliding_window")
-        if window is not None:
-            window = _need_int(d, "sliding_window")
+        eos_ids: Tuple[int, ...] = token_id_list(d.get("eos_token_id"), "eos_token_id")
+        # The reference never windows the layers of this architecture (only other families get a window,
+        # src/model.cpp:147), and folders of window-trained relatives that carry this architecture's name still
+        # hold a "sliding_window" number.  So the key alone changes nothing; the window applies only when the
+        # folder also says "use_sliding_window": true.
+        use_window = d.get("use_sliding_window", False)
+        if not isinstance(use_window, bool):
+            raise ConfigError(f"config.json: 'use_sliding_window' must be true or false, found {use_window!r}")
+        window = _need_int(d, "sliding_window") if use_window and d.get("sliding_window") is not None else None
         dtype = d.get("torch_dtype", d.get("dtype", "bfloat16"))
         if dtype not in ("bfloat16", "float32", "float16"):
             raise ConfigError(f"config.json: torch_dtype {dtype!r} is not supported (bfloat16, float32, float16)")
         known = {
             "architectures", "hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim", "hidden_act",
             "attention_bias", "mlp_bias", "partial_rotary_factor", "rms_norm_eps", "rope_theta", "eos_token_id",
-            "sliding_window", "torch_dtype", "dtype", "vocab_size", "num_hidden_layers", "intermediate_size",
+            "sliding_window", "use_sliding_window", "torch_dtype", "dtype", "vocab_size", "num_hidden_layers", "intermediate_size",
             "rope_scaling", "rope_parameters", "max_position_embeddings", "tie_word_embeddings", "bos_token_id",
         }
         return cls(
@@ -223,6 +193,7 @@ class LlamaConfig:
         }
         if self.sliding_window is not None:
             d["sliding_window"] = self.sliding_window
+            d["use_sliding_window"] = True
         if self.eos_token_ids:
             d["eos_token_id"] = list(self.eos_token_ids) if len(self.eos_token_ids) > 1 else self.eos_token_ids[0]
         if self.bos_token_id is not None:
@@ -277,18 +248,5 @@ class LlamaConfig:
                                       "tied": self.tie_word_embeddings}, head_weights),
             max_position=self.max_position_embeddings,
             stop_token_ids=self.eos_token_ids,
+            aliases={"lm_head.weight": "model.embed_tokens.weight"} if self.tie_word_embeddings else {},
         )
-
-
-def load_config_dict(model_dir: str) -> Dict[str, Any]:
-    path = os.path.join(model_dir, "config.json")
-    if not os.path.isfile(path):
-        raise ConfigError(f"{model_dir}: no config.json in the model folder")
-    with open(path, "r", encoding="utf-8") as f:
-        try:
-            d = json.load(f)
-        except json.JSONDecodeError as e:
-            raise ConfigError(f"{path}: not valid JSON ({e})") from None
-    if not isinstance(d, dict):
-        raise ConfigError(f"{path}: the top level must be an object")
-    return d

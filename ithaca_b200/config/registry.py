@@ -11,7 +11,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any, Callable, Dict, Optional
 
-from .llama import ConfigError, LlamaConfig, load_config_dict
+from .base import ConfigError, load_config_dict
+from .llama import LlamaConfig
 
 
 @dataclass(frozen=True)

@@ -70,6 +70,9 @@ class ModelSpec:
     head: PartSpec
     max_position: int
     stop_token_ids: Tuple[int, ...] = ()
+    # tensors a folder may hold although the model does not ask for them, because they repeat another one:
+    # name -> the tensor it must equal (a tied output matrix stored beside the embedding, for instance)
+    aliases: Dict[str, str] = field(default_factory=dict)
 
     def n_cache_entries(self) -> int:
         return 1 + max((e.cache for e in self.schedule), default=-1)

@@ -12,7 +12,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from . import build
-from .ops import KernelError, _check, _ptr, _stream
+from .ops import KernelError, _check, _ptr, _stream, sm_count
 
 _vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 _modules: Dict[int, ctypes.CDLL] = {}
@@ -20,10 +20,8 @@ _modules: Dict[int, ctypes.CDLL] = {}
 DECODE_CHUNK_PAGES = 4        # default: a decode block covers 4 pages = 256 keys; chunks start at multiples of that
 
 
-N_SM = 148
-
-
-def decode_chunk_pages(n_seqs: int, n_heads: int, n_kv_heads: int, max_kv_len: int, page_size: int = 64) -> int:
+def decode_chunk_pages(n_seqs: int, n_heads: int, n_kv_heads: int, max_kv_len: int, page_size: int = 64,
+                       n_sm: Optional[int] = None) -> int:
     """Pages per decode block.  Measured on B200 (head size 128, 8 kv heads, contexts 1k-16k, batches 1-64,
     chunks of 2-32 pages): the kernel is fastest with about two blocks per SM in ONE wave, so the pages of a
     sequence are cut into as many chunks as that allows, but into chunks of at least 4 pages (2 when even
@@ -32,6 +30,7 @@ def decode_chunk_pages(n_seqs: int, n_heads: int, n_kv_heads: int, max_kv_len: i
     are several waves anyway; a long chunk and a short rest then pack best (the short blocks of the last chunk
     start last and fill the tail).  Over 72 measured (batch, context) pairs the chunk picked here is within 1 % of
     the best one's time on average, 13 % at worst."""
+    N_SM = n_sm if n_sm is not None else sm_count()
     groups = n_seqs * n_kv_heads * -(-(n_heads // n_kv_heads) // 16)
     pages = max(1, -(-max_kv_len // page_size))
     if groups <= N_SM or groups > 1.5 * N_SM and groups <= 2 * N_SM:

@@ -111,6 +111,20 @@ __device__ __forceinline__ void ik_pdl_wait() { asm volatile("griddepcontrol.wai
 // it (not even a read-only one through `const __restrict__`) can be moved to before the wait.
 #define IK_AFTER_WAIT(ptr) asm volatile("" : "+l"(ptr))
 
+// Streaming multiprocessors of the current device (asked once per device).  Grids of persistent kernels, split
+// choices and scratch sizes follow it.
+static inline int ik_sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 // Kernel families, for IK_PDL=<bit mask>: which launches get the attribute.
 #define IK_FAMILY_ELEMENTWISE 1
 #define IK_FAMILY_SKINNY 2

@@ -152,7 +152,8 @@ IK_EXPORT int ik_swiglu(const float* gate_up, void* out, int out_dtype, int T, i
     if (T < 0 || ff <= 0) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
     const size_t total = (size_t)T * ff;
-    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    const int cap = ik_sm_count() * 16;
+    const int blocks = (int)((total + 255) / 256 < (size_t)cap ? (total + 255) / 256 : (size_t)cap);
     if (out_dtype == IK_F32)
         IK_RETURN_IF_ERROR(ik_launch(swiglu_kernel<float>, blocks, 256, 0, stream, gate_up, (float*)out, ff, total, interleaved));
     else if (out_dtype == IK_BF16)
@@ -310,3 +311,44 @@ IK_EXPORT int ik_rope_append(const float* qkv, void* q_out, int q_dtype, void* k
 #undef IK_ROPE
     IK_LAUNCH_STATUS();
 }
+
+// ------------------------------------------------------------------ random weights
+// out[i] = offset + scale * (sum of the eight 16-bit fields of two 64-bit hash words - 262140), i the flat index.
+// The words are the outputs 2i+1 and 2i+2 of the splitmix64 sequence that starts at `key`.  The sum of eight
+// uniform 16-bit integers is close to a normal law (Irwin-Hall, standard deviation 53510.85...) and is formed
+// with integer arithmetic and one float multiply and add, so the host (numpy) and this kernel give the same
+// bits: a model made on the device has exactly the weights a folder written on the host from the same
+// configuration and seed holds.
+__device__ __forceinline__ unsigned long long ik_mix64(unsigned long long z) {
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+template <typename TO>
+__global__ void fill_random_kernel(TO* __restrict__ out, size_t n, unsigned long long key, float scale, float offset) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        int s = 0;
+        #pragma unroll
+        for (int j = 1; j <= 2; j++) {
+            const unsigned long long h = ik_mix64(key + (2ull * i + j) * 0x9E3779B97F4A7C15ull);
+            s += (int)(h & 0xFFFF) + (int)((h >> 16) & 0xFFFF) + (int)((h >> 32) & 0xFFFF) + (int)(h >> 48);
+        }
+        ik_st(out, i, __fadd_rn(offset, __fmul_rn(scale, (float)(s - 262140))));
+    }
+}
+
+IK_EXPORT int ik_fill_random(void* out, int out_dtype, unsigned long long n, unsigned long long key, float scale, float offset,
+                             cudaStream_t stream) {
+    if (n == 0) return IK_OK;
+    const unsigned long long cap = (unsigned long long)ik_sm_count() * 16;
+    const int blocks = (int)((n + 1023) / 1024 < cap ? (n + 1023) / 1024 : cap);
+    if (out_dtype == IK_F32) fill_random_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, (size_t)n, key, scale, offset);
+    else if (out_dtype == IK_BF16) fill_random_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)out, (size_t)n, key, scale, offset);
+    else return IK_BAD_ARGUMENT;
+    IK_LAUNCH_STATUS();
+}
+
+// Streaming multiprocessors of the current device, for the host side's choices of splits and chunks.
+IK_EXPORT int ik_device_sm_count() { return ik_sm_count(); }

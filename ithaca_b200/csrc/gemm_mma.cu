@@ -193,7 +193,7 @@ int launch_skinny(const void* X, const void* W, void* Y, int M, int N, int K, in
 // The deeper unroll (more bytes in flight, 2 blocks per SM instead of 3) pays unless the grid then fills
 // its last wave of blocks badly.  Depends on N only, so a row's summation order does not depend on M.
 bool deep_unroll_pays(int N) {
-    const int blocks = (N + 15) / 16, slots = 2 * 148;
+    const int blocks = (N + 15) / 16, slots = 2 * ik_sm_count();
     const int waves = (blocks + slots - 1) / slots;
     return (double)blocks / ((double)waves * slots) >= 0.8;
 }

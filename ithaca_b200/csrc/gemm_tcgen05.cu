@@ -52,9 +52,12 @@ template <int BN> struct Cfg {
     static constexpr int SMEM = STAGES * STAGE + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
-constexpr int MAX_BLOCKS = 148;                                       // one persistent block per SM
-constexpr size_t IK_SK_PIECE_FLOATS = (size_t)MAX_BLOCKS * 256 * BM;  // stream-K scratch: a [256][128] piece per block ...
-constexpr size_t IK_SK_BYTES = IK_SK_PIECE_FLOATS * 4 + MAX_BLOCKS * 4 * 4;   // ... then a flag per block and epilogue warp
+// Persistent: one block per SM of the device.  Stream-K scratch: a flag per block and epilogue warp (room for 1024
+// blocks), then a [256][128] piece of raw sums per block.
+constexpr int SK_MAX_BLOCKS = 1024;
+constexpr size_t SK_FLAG_INTS = (size_t)SK_MAX_BLOCKS * 4;
+inline int max_blocks() { const int n = ik_sm_count(); return n < SK_MAX_BLOCKS ? n : SK_MAX_BLOCKS; }
+inline size_t stream_k_bytes() { return SK_FLAG_INTS * 4 + (size_t)max_blocks() * 256 * BM * 4; }
 
 // One accumulator's worth of work: K steps [kb0, kb0 + nkb) of output tile (nt, mt).
 struct Work {
@@ -188,8 +191,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     ik_pdl_launch_dependents();
 
     float* const slice_sums = stream_k ? nullptr : partial;           // data-parallel K slices: [slice][M][N]
-    float* const pieces = stream_k ? partial : nullptr;               // stream-K: [block][BN][128] raw sums of a piece
-    int* const piece_flags = stream_k ? reinterpret_cast<int*>(partial + IK_SK_PIECE_FLOATS) : nullptr;   // [block][4]
+    int* const piece_flags = stream_k ? reinterpret_cast<int*>(partial) : nullptr;                        // [block][4]
+    float* const pieces = stream_k ? partial + SK_FLAG_INTS : nullptr;  // stream-K: [block][BN][128] raw sums of a piece
 
     if (warp == 0) {
         if (lane == 0) {
@@ -480,7 +483,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial
     const long long tiles = (long long)((N + BM - 1) / BM) * ((M + BN - 1) / BN);
     if (splits == 0) {                  // stream-K: equal shares of all (tile, K step) units, at least four K steps a block
         const long long units = tiles * nkb;
-        const int blocks = (int)(units / 4 < 1 ? 1 : units / 4 < MAX_BLOCKS ? units / 4 : MAX_BLOCKS);
+        const int blocks = (int)(units / 4 < 1 ? 1 : units / 4 < max_blocks() ? units / 4 : max_blocks());
         IK_RETURN_IF_ERROR(ik_launch(kern, blocks, THREADS, C::SMEM, stream, mw, mx, (TY*)Y, partial, M, N, K, ldy, accumulate,
                                      swiglu, nkb, 1, 1, status, rope));
         return (int)cudaGetLastError();
@@ -488,14 +491,15 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial
     const int per = (nkb + splits - 1) / splits;
     const int n_splits = (nkb + per - 1) / per;
     const long long total = tiles * n_splits;
-    const int blocks = (int)(total < MAX_BLOCKS ? total : MAX_BLOCKS);
+    const int blocks = (int)(total < max_blocks() ? total : max_blocks());
     IK_RETURN_IF_ERROR(ik_launch(kern, blocks, THREADS, C::SMEM, stream, mw, mx, (TY*)Y, n_splits > 1 ? partial : nullptr, M,
                                  N, K, ldy, accumulate, swiglu, per, n_splits, 0, status, rope));
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (n_splits > 1) {
         const size_t elems = (size_t)M * N;
-        const int rblocks = (int)((elems + 255) / 256 < 148 * 8 ? (elems + 255) / 256 : 148 * 8);
+        const size_t rcap = (size_t)ik_sm_count() * 8;
+        const int rblocks = (int)((elems + 255) / 256 < rcap ? (elems + 255) / 256 : rcap);
         IK_RETURN_IF_ERROR(ik_launch(splitk_reduce_kernel<TY>, rblocks, 256, 0, stream, partial, (TY*)Y, M, N, ldy, n_splits, accumulate, swiglu, rope));
         e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
@@ -509,7 +513,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial
 IK_EXPORT int ik_gemm_tcgen05_tile(int M) { return M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 
 // Scratch of the stream-K mode, in bytes: zeroed once by the caller, then left to the kernels (one stream at a time).
-IK_EXPORT int ik_gemm_tcgen05_stream_k_bytes() { return (int)IK_SK_BYTES; }
+IK_EXPORT int ik_gemm_tcgen05_stream_k_bytes() { return (int)stream_k_bytes(); }
 
 // splits > 1 needs `partial`: splits * M * N floats of scratch owned by the caller.
 // splits == 0 is the stream-K mode; `partial` is then the scratch described above.

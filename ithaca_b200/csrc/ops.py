@@ -70,6 +70,8 @@ _SIGNATURES = {
     "ik_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _f, _vp, _vp],
     "ik_rmsnorm": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
     "ik_swiglu": [_vp, _vp, _i, _i, _i, _i, _vp],
+    "ik_fill_random": [_vp, _i, _u64, _u64, _f, _f, _vp],
+    "ik_device_sm_count": [],
     "ik_rope_append": [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "ik_gemm_bf16_mma": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
@@ -155,6 +157,15 @@ def swiglu(gate_up: torch.Tensor, out_dtype: torch.dtype, out: Optional[torch.Te
     return out
 
 
+def fill_random(out: torch.Tensor, key: int, scale: float, offset: float) -> torch.Tensor:
+    """Fills ``out`` with offset + scale * (a centred sum of eight 16-bit hash fields) per flat index; the values are
+    the ones ``weights.random_init.hashed_normal`` gives on the host for the same key."""
+    _need(out, "out")
+    _check(lib().ik_fill_random(_ptr(out), _code(out), out.numel(), key & 0xFFFFFFFFFFFFFFFF, scale, offset, _stream()),
+           "fill_random")
+    return out
+
+
 def rope_append(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                 token_seq: torch.Tensor, token_pos: torch.Tensor, table: torch.Tensor,
                 inv_freq: Optional[torch.Tensor], n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
@@ -228,7 +239,17 @@ def gemm_bf16_mma(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] 
     return out
 
 
-N_SM = 148
+_sm_counts = {}
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device (asked once per device)."""
+    dev = torch.cuda.current_device()
+    n = _sm_counts.get(dev)
+    if n is None:
+        n = _sm_counts[dev] = int(lib().ik_device_sm_count())
+    return n
+
 
 _stream_k_scratch = {}
 
@@ -250,6 +271,7 @@ def tcgen05_splits(M: int, N: int, K: int) -> int:
     Measured on B200 with 4096 x 4096 .. 28672 x 4096 weights: with fewer tiles than half the SMs, K
     slices win; stream-K wins when whole tiles would leave more than a tenth of the SMs' time unused
     and there is one token tile of at most 128 tokens (bandwidth-bound); beyond that whole tiles win."""
+    N_SM = sm_count()
     tile_m = lib().ik_gemm_tcgen05_tile(M)
     tiles_m = -(-M // tile_m)
     tiles = -(-N // 128) * tiles_m

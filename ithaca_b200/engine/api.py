@@ -32,13 +32,15 @@ def _round_up(n: int, m: int) -> int:
 class Engine:
     def __init__(self, model_dir: Optional[str] = None, *, dtype: str = "bfloat16", device: str = "cuda:0",
                  max_tokens: Optional[int] = None, max_slots: Optional[int] = None, ctx: Optional[int] = None, graphs: bool = True,
-                 _model=None, _config=None):
+                 max_step_tokens: Optional[int] = 16384, _model=None, _config=None):
         """``max_tokens``: the most positions live sequences hold at any time, each rounded up
         to a multiple of 64; it sizes the cache (default: 8 sequences of ``ctx``).
         ``ctx``: the most positions one sequence may hold (default: the model's
         ``max_position_embeddings``, as the reference caps ``--ctx`` at the trained
         context, src/model.cpp:259).  ``graphs``: replay decode steps of the generation
-        loop from CUDA graphs."""
+        loop from CUDA graphs.  ``max_step_tokens``: the most tokens one pass over the model
+        takes (it bounds the activations' memory); a step that brings more, such as a batch of
+        long prompts, is run as several passes with the same result (None: no limit)."""
         if not torch.cuda.is_available():
             raise RuntimeError("ithaca_b200 runs on a CUDA device only; none is available")
         torch.cuda.set_device(device)
@@ -54,7 +56,7 @@ class Engine:
             max_tokens = 8 * _round_up(min(self.context_length, 4096), PAGE_SIZE)
         self.cache = SequenceCache(self.model.cache_requests(), max_tokens=max_tokens, max_slots=max_slots,
                                    kv_dtype=self.runtime.kv_dtype, device=device)
-        self.stepper = Stepper(self.model, self.cache, max_position=self.context_length)
+        self.stepper = Stepper(self.model, self.cache, max_position=self.context_length, max_step_tokens=max_step_tokens)
         self.last_stats: Optional[GenStats] = None
         self._sampler: Optional[Sampler] = None
         self._decoder = GraphDecoder(self.stepper) if graphs and getattr(self.model, "graph_safe", False) else None
@@ -87,6 +89,21 @@ class Engine:
     def free_slot(self, slot: int) -> None:
         self._settle()
         self.cache.free_slot(slot)
+
+    def truncate(self, slot: int, n: int) -> None:
+        """Keeps the first ``n`` positions of the slot's sequence; the next step's tokens follow them
+        (the reference's ``rewind``, src/model.cpp:1047-1058, which its chat loop uses to keep the
+        cache of a prefix that the next prompt shares, src/chat.cpp:311-318).  What lay behind is
+        overwritten by the tokens fed next and is never read before that.  A sequence whose layers
+        keep a fixed-size state can only go back to 0; a windowed group refuses to go back behind
+        pages it has released.  On refusal nothing has changed."""
+        self._settle()
+        self.cache.truncate(slot, n)
+
+    def length(self, slot: int) -> int:
+        """Positions the slot's sequence holds."""
+        self._settle()
+        return self.cache.length(slot)
 
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
              want: Union[str, None, Sequence[Sequence[int]]] = "last") -> Optional[torch.Tensor]:

@@ -15,21 +15,34 @@ import torch
 from ..cache.cache import SequenceCache
 from ..config import ConfigError, config_from_model_dir
 from ..config.spec import ModelSpec, validate_schedule
-from ..parts import BLOCKS, NORMS, Runtime
+from ..parts import BLOCKS, EMBEDDINGS, HEADS, NORMS, Runtime
 from ..parts.block import _merge
-from ..parts.embedding import Embedding, OutputHead
 from ..weights.loader import TensorReq, WeightError, check_tensors, load_checkpoint, read_model_tensors, _storage_form
 
 
 def weight_manifest(spec: ModelSpec) -> Dict[str, TensorReq]:
     """Every tensor the model needs, with its shape."""
     out: Dict[str, TensorReq] = {}
-    _merge(out, Embedding.manifest(spec.embedding))
+    _merge(out, EMBEDDINGS.get(spec.embedding.kind).manifest(spec.embedding))
     for b in spec.layers:
         _merge(out, BLOCKS.get(b.kind).manifest(b))
     _merge(out, NORMS.get(spec.final_norm.kind).manifest(spec.final_norm))
-    _merge(out, OutputHead.manifest(spec.head))
+    _merge(out, HEADS.get(spec.head.kind).manifest(spec.head))
     return out
+
+
+def streamed_tensor_names(spec: ModelSpec) -> List[str]:
+    """The tensors a step reads in full whatever it brings: what the layers' mixers and feed-forwards and the
+    head ask for (their manifests), each once.  Norm vectors are left out (a few KB), and so is the embedding
+    matrix, of which a step reads one row per token, unless the head shares it."""
+    names: List[str] = []
+    for e in spec.schedule:
+        b = spec.layers[e.layer]
+        from ..parts import FEED_FORWARDS, MIXERS
+        for part, reg in ((b.mixer, MIXERS), (b.feed_forward, FEED_FORWARDS)):
+            names += list(reg.get(part.kind).manifest(part))
+    names += list(HEADS.get(spec.head.kind).manifest(spec.head))
+    return list(dict.fromkeys(names))
 
 
 class DecoderModel:
@@ -37,13 +50,21 @@ class DecoderModel:
         validate_schedule(spec)
         self.spec = spec
         self.runtime = runtime
-        self.embedding = Embedding(spec.embedding, tensors, runtime)
+        # bytes of the matrices a step streams, in the form the kernels read them: 16-bit on the bfloat16 path
+        # (a matrix stored in 32-bit is rounded once when it is loaded), as stored on the float32 path
+        self._streamed_bytes = sum(
+            tensors[n].numel() * (2 if runtime.dtype == "bfloat16" and tensors[n].dtype.is_floating_point
+                                  else tensors[n].element_size())
+            for n in streamed_tensor_names(spec) if n in tensors)
+        self.embedding = EMBEDDINGS.get(spec.embedding.kind)(spec.embedding, tensors, runtime)
         self.layers = [BLOCKS.get(b.kind)(b, tensors, runtime) for b in spec.layers]
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, tensors, runtime)
-        if spec.head.weights["weight"] == spec.embedding.weights["weight"]:
+        shared = set(spec.head.weights.values()) & set(spec.embedding.weights.values())
+        if shared and hasattr(self.embedding, "table"):
             tensors = dict(tensors)
-            tensors[spec.head.weights["weight"]] = self.embedding.table      # one copy on the device for both
-        self.head = OutputHead(spec.head, tensors, runtime)
+            for name in shared:
+                tensors[name] = self.embedding.table                        # one copy on the device for both
+        self.head = HEADS.get(spec.head.kind)(spec.head, tensors, runtime)
 
     @property
     def graph_safe(self) -> bool:
@@ -63,7 +84,7 @@ class DecoderModel:
     def forward(self, ctx, cache: SequenceCache) -> Optional[torch.Tensor]:
         """Runs the step's tokens through every scheduled run; returns float32 logits
         [wanted rows, vocab], or None when no row is wanted."""
-        h = self.embedding.forward(ctx.token_ids)
+        h = self.embedding.forward(ctx.token_ids, ctx)
         for e in self.spec.schedule:
             self.layers[e.layer].forward(h, ctx, cache.layer(e.cache), e.writes_cache)
         if ctx.n_logit_rows == 0:
@@ -72,22 +93,9 @@ class DecoderModel:
         return self.head.forward(xn)
 
     def weight_bytes(self) -> int:
-        """Bytes of weights a step reads once (matrices and the head; for roofline figures)."""
-        seen, total = set(), 0
-
-        def add(t: torch.Tensor):
-            nonlocal total
-            if t.data_ptr() not in seen:
-                seen.add(t.data_ptr())
-                total += t.numel() * t.element_size()
-
-        for layer in self.layers:
-            for part in (layer.mixer, layer.feed_forward):
-                for v in vars(part).values():
-                    if hasattr(v, "weight") and isinstance(v.weight, torch.Tensor):
-                        add(v.weight)
-        add(self.head.linear.weight)
-        return total
+        """Bytes of weights a step reads once (the matrices of the scheduled layers and the head, each
+        counted once; for roofline figures)."""
+        return self._streamed_bytes
 
 
 def build_model(arch, config, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
@@ -106,15 +114,14 @@ def load_model(model_dir: str, runtime: Runtime):
     manifest = weight_manifest(spec)
     found = read_model_tensors(model_dir)
     ignore = []
-    head_name, emb_name = spec.head.weights["weight"], spec.embedding.weights["weight"]
-    if head_name == emb_name and "lm_head.weight" in found and "lm_head.weight" not in manifest:
-        # a tied model may still store the head; it must then be the embedding matrix itself
-        if emb_name in found and found["lm_head.weight"].shape == found[emb_name].shape and \
-                torch.equal(found["lm_head.weight"], found[emb_name]):
-            ignore.append("lm_head.weight")
-        else:
-            raise WeightError("the configuration ties the output head to the embedding, but the folder holds a "
-                              "different 'lm_head.weight'")
+    for name, same_as in spec.aliases.items():
+        if name in found and name not in manifest:
+            # a tensor that repeats another one may be stored; it must then hold the same values
+            if same_as in found and found[name].shape == found[same_as].shape and torch.equal(found[name], found[same_as]):
+                ignore.append(name)
+            else:
+                raise WeightError(f"the configuration says that '{name}' repeats '{same_as}', but the folder holds a "
+                                  f"different '{name}'")
     check_tensors(found, manifest, ignore)
     tensors = {n: _storage_form(n, found[n], manifest[n]) for n in manifest if n in found}
     return build_model(arch, config, tensors, runtime), config

@@ -27,7 +27,16 @@ class StepError(ValueError):
 
 
 class Stepper:
-    def __init__(self, model, cache: SequenceCache, max_position: Optional[int] = None):
+    def __init__(self, model, cache: SequenceCache, max_position: Optional[int] = None,
+                 max_step_tokens: Optional[int] = None):
+        """``max_step_tokens``: the workspace limit.  A step that brings more tokens is run as
+        several passes of at most that many, cut along the token-major order; the result is the
+        same (bit for bit in float32, to rounding in bfloat16).  The reference cuts a prompt into
+        pieces of at most 512 tokens (src/model.cpp:1364-1368)."""
+        if max_step_tokens is not None and max_step_tokens < 1:
+            raise ValueError("max_step_tokens must be positive")
+        self.max_step_tokens = max_step_tokens
+        self.passes_last_step = 0
         self.model = model
         self.cache = cache
         self.runtime = model.runtime
@@ -92,9 +101,56 @@ class Stepper:
              want: Union[str, None, Sequence[Sequence[int]]] = "last") -> Optional[torch.Tensor]:
         """Runs the tokens and returns float32 logits [wanted, vocab] on the device (None if
         nothing is wanted), rows in the order of the slots and of each slot's wanted places."""
+        if self.max_step_tokens is not None and sum(len(t) for t in tokens) > self.max_step_tokens:
+            return self._step_in_passes(slots, tokens, want)
         ctx = self.prepare(slots, tokens, want)
         logits = self.model.forward(ctx, self.cache)
         self.finish(ctx)
+        self.passes_last_step = 1
+        return logits
+
+    def _step_in_passes(self, slots, tokens, want) -> Optional[torch.Tensor]:
+        """A step over the workspace limit: the flat token list is cut every ``max_step_tokens`` tokens;
+        each pass runs its pieces of sequences as an ordinary step behind what the passes before left
+        in the cache.  Everything is checked and every page taken before the first pass runs."""
+        want_lists = self._validate(slots, tokens, want)
+        self.cache.reserve(slots, [len(t) for t in tokens])
+        limit = self.max_step_tokens
+        passes: List[List[tuple]] = [[]]                    # per pass: (sequence index, first token, end)
+        room = limit
+        for b, t in enumerate(tokens):
+            lo = 0
+            while lo < len(t):
+                if room == 0:
+                    passes.append([])
+                    room = limit
+                hi = min(len(t), lo + room)
+                passes[-1].append((b, lo, hi))
+                room -= hi - lo
+                lo = hi
+        outs: List[torch.Tensor] = []
+        where = {}                                          # (sequence, index in its want list) -> row of the passes' outputs
+        row = 0
+        for pieces in passes:
+            piece_want = []
+            for b, lo, hi in pieces:
+                idx = [i for i, w in enumerate(want_lists[b]) if lo <= w < hi]
+                piece_want.append([want_lists[b][i] - lo for i in idx])
+                for i in idx:
+                    where[(b, i)] = row
+                    row += 1
+            ctx = self.prepare([slots[b] for b, _, _ in pieces], [tokens[b][lo:hi] for b, lo, hi in pieces], piece_want)
+            out = self.model.forward(ctx, self.cache)
+            self.finish(ctx)
+            if out is not None:
+                outs.append(out)
+        self.passes_last_step = len(passes)
+        if not outs:
+            return None
+        logits = outs[0] if len(outs) == 1 else torch.cat(outs, 0)
+        order = [where[(b, i)] for b in range(len(tokens)) for i in range(len(want_lists[b]))]
+        if order != list(range(len(order))):
+            logits = logits[torch.as_tensor(order, dtype=torch.long, device=logits.device)]
         return logits
 
     def check_status(self) -> None:

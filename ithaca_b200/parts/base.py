@@ -21,6 +21,10 @@ method that states the tensors it needs with their shapes, and a constructor
 * feed-forward:  ``forward(x, ctx, residual)``: adds its output into ``residual``.
 * block:         ``forward(residual, ctx, cache, writes_cache)``: arranges norms, mixer and
                  feed-forward around the residual stream.
+* embedding:     ``forward(ids[T] int32, ctx) -> [T, d]`` float32 (the residual stream's start); it has
+                 ``table``, the matrix a tied head shares.
+* head:          ``forward(xn[rows, d]) -> [rows, vocab]`` float32 logits; ``weight_names()`` lists the
+                 tensors it reads in full at every step.
 """
 from __future__ import annotations
 
@@ -88,12 +92,16 @@ POSITIONS = Registry("position")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 BLOCKS = Registry("block")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("head")
 
 register_norm = NORMS.register
 register_position = POSITIONS.register
 register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register
 register_block = BLOCKS.register
+register_embedding = EMBEDDINGS.register
+register_head = HEADS.register
 
 
 def to_device(t: torch.Tensor, runtime: Runtime) -> torch.Tensor:

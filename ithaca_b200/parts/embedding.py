@@ -14,7 +14,7 @@ import torch
 from ..config.spec import PartSpec
 from ..csrc import ops
 from ..weights.loader import TensorReq
-from .base import Runtime, to_device
+from .base import Runtime, register_embedding, register_head, to_device
 from .linear import Linear
 
 
@@ -30,7 +30,7 @@ class Embedding:
         self.table = to_device(tensors[spec.weights["weight"]], runtime).contiguous()
         self.runtime = runtime
 
-    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+    def forward(self, ids: torch.Tensor, ctx=None) -> torch.Tensor:
         return ops.embed(ids, self.table, self.scale, self.runtime.status)
 
 
@@ -45,3 +45,7 @@ class OutputHead:
 
     def forward(self, xn: torch.Tensor) -> torch.Tensor:
         return self.linear(xn, out_dtype=torch.float32)
+
+
+register_embedding("embedding", Embedding)
+register_head("lm_head", OutputHead)

@@ -135,7 +135,9 @@ def attention_block(xn: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, c
     v = (xn @ w[f"{prefix}.v_proj.weight"].to(dt).T).view(T, nkv, hd)
     q = rope(q, positions, inv_freq)
     k = rope(k, positions, inv_freq)
-    att = attention(q, k, v, window=cfg.get("sliding_window"))
+    # the window applies only where the folder switches it on: the reference runs this architecture without one
+    # (src/model.cpp:147 sets a window for other families only)
+    att = attention(q, k, v, window=cfg.get("sliding_window") if cfg.get("use_sliding_window") else None)
     return att.reshape(T, nh * hd) @ w[f"{prefix}.o_proj.weight"].to(dt).T
 
 

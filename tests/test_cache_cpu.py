@@ -108,6 +108,17 @@ def test_a_window_releases_pages_no_query_can_reach():
     assert t.tables[0][s][3] == -1 and t.pools[0].n_free == 4
     with pytest.raises(CacheError, match="released"):
         t.truncate(s, 200)
+    assert t.length[s] == 360                      # a refusal changes nothing
+    with pytest.raises(CacheError, match="released"):
+        t.truncate(s, 330)                         # position 330 reaches back to 231, which lay in page 3
+    t.truncate(s, 356)                             # position 356 reaches back to 257: page 4 is still there
+    assert t.length[s] == 356
+    t.reserve(s, 30); t.commit(s, 30)
+    t.check_consistent()
+    t.truncate(s, 0)                               # back to the start: every page goes back, the slot stays
+    assert t.length[s] == 0 and t.pools[0].n_free == 6 and t.in_use(s)
+    t.reserve(s, 130); t.commit(s, 130)
+    assert list(t.tables[0][s][:3] >= 0) == [True, True, True]
     t.check_consistent()
     t.free_slot(s)
     assert t.pools[0].n_free == 6

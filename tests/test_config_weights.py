@@ -3,6 +3,7 @@ import json
 import os
 import struct
 
+import numpy as np
 import pytest
 import torch
 
@@ -205,3 +206,54 @@ def test_tensor_in_two_files_and_missing_folder(tmp_path):
         read_model_tensors(d)
     with pytest.raises(ConfigError, match="no config.json"):
         config_from_model_dir(d)
+
+
+def test_random_weights_are_a_function_of_seed_name_and_index():
+    """Element i of a tensor depends on (seed, name, i) only: a slice made alone equals the slice of the whole,
+    another name or seed gives other values, and the law is close to the normal one asked for."""
+    from ithaca_b200.weights.random_init import hashed_normal, random_tensor, tensor_key
+    k = tensor_key(7, "model.layers.3.mlp.up_proj.weight")
+    whole = hashed_normal(k, 300000, 0.02)
+    assert np.array_equal(whole[1234:5000], hashed_normal(k, 5000 - 1234, 0.02, first=1234))
+    assert not np.array_equal(whole[:100], hashed_normal(tensor_key(8, "model.layers.3.mlp.up_proj.weight"), 100, 0.02))
+    assert not np.array_equal(whole[:100], hashed_normal(tensor_key(7, "model.layers.3.mlp.gate_proj.weight"), 100, 0.02))
+    assert abs(whole.mean()) < 2e-4 and abs(whole.std() - 0.02) < 2e-4 and np.abs(whole).max() < 0.1
+    z = whole / 0.02
+    assert abs((z ** 3).mean()) < 0.03 and abs((z ** 4).mean() - 3.0) < 0.2       # skewness 0, fourth moment near 3
+    # one value by hand: the two hash words' eight 16-bit fields, centred and scaled in float32
+    def mix(v):
+        v = ((v ^ (v >> 30)) * 0xBF58476D1CE4E5B9) & (2 ** 64 - 1)
+        v = ((v ^ (v >> 27)) * 0x94D049BB133111EB) & (2 ** 64 - 1)
+        return v ^ (v >> 31)
+    i, s = 4321, 0
+    for j in (1, 2):
+        h = mix((k + (2 * i + j) * 0x9E3779B97F4A7C15) & (2 ** 64 - 1))
+        s += sum((h >> sh) & 0xFFFF for sh in (0, 16, 32, 48))
+    scale = np.float32(0.02 / np.sqrt(8 * (65536.0 ** 2 - 1) / 12))
+    assert whole[i] == np.float32(scale * np.float32(s - 262140))
+    ones = random_tensor("n", TensorReq((64,), init="ones"), 1, "float32")
+    assert abs(ones.mean().item() - 1.0) < 0.01 and 0.002 < ones.std().item() < 0.02
+
+
+def test_generation_config_adds_stop_ids(tmp_path):
+    d = write_random_model(str(tmp_path / "m"), TINY_A, seed=1)
+    assert config_from_model_dir(d)[1].eos_token_ids == (7,)
+    with open(os.path.join(d, "generation_config.json"), "w") as f:
+        json.dump({"eos_token_id": [9, 7, 11], "temperature": 0.6}, f)
+    cfg = config_from_model_dir(d)[1]
+    assert cfg.eos_token_ids == (7, 9, 11) and cfg.model_spec().stop_token_ids == (7, 9, 11)
+    with open(os.path.join(d, "generation_config.json"), "w") as f:
+        json.dump({"eos_token_id": "</s>"}, f)
+    with pytest.raises(ConfigError, match="generation_config.json"):
+        config_from_model_dir(d)
+
+
+def test_a_window_needs_to_be_switched_on():
+    """The reference runs this architecture without a window; a folder that merely carries the number keeps every key."""
+    base = dict(TINY_A, sliding_window=40)
+    assert config_from_dict(base)[1].sliding_window is None
+    on = config_from_dict(dict(base, use_sliding_window=True))[1]
+    assert on.sliding_window == 40 and on.model_spec().layers[0].mixer["window"] == 40
+    assert on.to_dict()["use_sliding_window"] is True and config_from_dict(on.to_dict())[1] == on
+    with pytest.raises(ConfigError, match="use_sliding_window"):
+        config_from_dict(dict(base, use_sliding_window="yes"))

@@ -127,13 +127,13 @@ def test_decode_chunk_choice_is_sane():
     """Pages per decode-attention block: between 1 and the sequence's pages, the headline shape keeps its measured
     optimum, and the number of chunks never exceeds what the scratch is sized for."""
     from ithaca_b200.csrc.attention_bf16 import decode_chunk_pages
-    assert decode_chunk_pages(8, 32, 8, 4096) == 16
-    assert decode_chunk_pages(1, 32, 8, 4096) == 4
+    assert decode_chunk_pages(8, 32, 8, 4096, n_sm=148) == 16
+    assert decode_chunk_pages(1, 32, 8, 4096, n_sm=148) == 4
     for n_seqs in (1, 2, 3, 7, 8, 16, 24, 33, 64, 200):
         for heads, kv in ((32, 8), (4, 4), (6, 2), (40, 40), (64, 1)):
             for length in (1, 63, 64, 65, 700, 4096, 20000):
                 pages = -(-length // 64)
-                c = decode_chunk_pages(n_seqs, heads, kv, length)
+                c = decode_chunk_pages(n_seqs, heads, kv, length, n_sm=148)
                 assert 1 <= c <= max(pages, 2), (n_seqs, heads, kv, length, c)
 
 

@@ -78,7 +78,8 @@ def test_attention_part_prompt_then_tokens(dtype, window):
     slot = cache.alloc_slot()
     x = torch.randn(T, d).to(rt.act_dtype)
     # plain: the whole sequence at once
-    cfg = {"num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": hd, "sliding_window": window}
+    cfg = {"num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": hd, "sliding_window": window,
+           "use_sliding_window": window is not None}
     w = {f"p.{k}_proj.weight": v for k, v in t.items()}
     ref = P.attention_block(x.double(), w, "p", cfg, P.rope_inv_freq(hd, 1000.0, None), torch.arange(T))
     # part: 60 tokens in one step, then 15 one by one

@@ -32,6 +32,7 @@ def random_config(seed):
            "tie_word_embeddings": bool(rng.integers(0, 2)), "torch_dtype": str(rng.choice(["bfloat16", "float32"]))}
     if rng.integers(0, 2) == 0:
         cfg["sliding_window"] = int(rng.choice([8, 40, 100, 300]))
+        cfg["use_sliding_window"] = True
     return cfg
 
 
@@ -39,7 +40,7 @@ def random_config(seed):
 NARROW_WINDOW = {"architectures": ["LlamaForCausalLM"], "hidden_size": 72, "num_hidden_layers": 2, "num_attention_heads": 20,
                  "num_key_value_heads": 5, "head_dim": 128, "intermediate_size": 328, "vocab_size": 256, "rope_theta": 10000.0,
                  "rope_scaling": None, "rms_norm_eps": 1e-5, "max_position_embeddings": 1400, "tie_word_embeddings": True,
-                 "torch_dtype": "bfloat16", "sliding_window": 40}
+                 "torch_dtype": "bfloat16", "sliding_window": 40, "use_sliding_window": True}
 
 
 _PLAIN = {}      # case -> what the plain implementation says (computed once for both dtypes)

@@ -23,7 +23,7 @@ TINY_C = {   # head size 48 (a step of 16, no power of two), hidden != heads*hea
     "architectures": ["LlamaForCausalLM"], "hidden_size": 200, "num_hidden_layers": 2, "num_attention_heads": 5,
     "num_key_value_heads": 1, "head_dim": 48, "intermediate_size": 328, "vocab_size": 301, "rope_theta": 25000.0,
     "rope_scaling": {"rope_type": "linear", "factor": 2.0}, "rms_norm_eps": 3e-6, "max_position_embeddings": 512,
-    "tie_word_embeddings": False, "torch_dtype": "bfloat16", "sliding_window": 40,
+    "tie_word_embeddings": False, "torch_dtype": "bfloat16", "sliding_window": 40, "use_sliding_window": True,
 }
 TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
 
