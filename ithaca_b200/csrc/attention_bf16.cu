@@ -100,7 +100,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     }
     auto load_page = [&](int stage, int p) {
         int page = table[(size_t)b * table_stride + p];
-        if (page < 0 || page >= n_pages) { if (threadIdx.x == 0 && status) atomicExch(status, 3); page = 0; }
+        if (page < 0 || page >= n_pages) { if (threadIdx.x == 0) ik_set_status(status, IK_STATUS_READ_NO_PAGE); page = 0; }
         const bf16* kg = k_pages + ((size_t)page * nkv + kvh) * PAGE * HD;
         const bf16* vg = v_pages + ((size_t)page * nkv + kvh) * PAGE * HD;
         bf16* ks = Ks + stage * PAGE * LD;
@@ -268,7 +268,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int q_begin = cu_seqlens[b], n_new = cu_seqlens[b + 1] - q_begin;
     const int row0 = tile * TC_BM;
     if (row0 >= n_new) return;
-    if (status && *(volatile int*)status == IK_STATUS_GEMM_TIMEOUT) return;
+    if (ik_status_has(status, IK_STATUS_GEMM_TIMEOUT)) return;
     const int kv_len = kv_lens[b], start = kv_len - n_new;
     const int rows = min(TC_BM, n_new - row0);
     const int pos_lo = start + row0, pos_hi = pos_lo + rows - 1;
@@ -279,7 +279,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // The swizzled tiles need 1024-byte alignment.  Dynamic shared memory of a kernel without static shared
     // memory starts on such a boundary; should it ever not, the block reports it instead of computing garbage.
     if (smem_u32(tc_smem) & 1023) {
-        if (threadIdx.x == 0 && status) atomicExch(status, 5);
+        if (threadIdx.x == 0) ik_set_status(status, IK_STATUS_SMEM_ALIGN);
         return;
     }
     unsigned char* Qs = tc_smem;
@@ -328,7 +328,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 tma_load_2d(Qs + bx * (TC_BM * 128), &map_q, h * HD + bx * 64, q_begin + row0, q_full);
             auto page_row = [&](int i) -> int {
                 int page = table[(size_t)b * table_stride + p_lo + i];
-                if (page < 0 || page >= n_pages) { if (status) atomicExch(status, 3); page = 0; }
+                if (page < 0 || page >= n_pages) { ik_set_status(status, IK_STATUS_READ_NO_PAGE); page = 0; }
                 return (page * nkv + kvh) * PAGE;
             };
             // keys of page i, then values of page i - 1
@@ -550,7 +550,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
     }
     auto load_page = [&](int stage, int p) {
         int page = table[(size_t)b * table_stride + p];
-        if (page < 0 || page >= n_pages) { if (threadIdx.x == 0 && status) atomicExch(status, 3); page = 0; }
+        if (page < 0 || page >= n_pages) { if (threadIdx.x == 0) ik_set_status(status, IK_STATUS_READ_NO_PAGE); page = 0; }
         const bf16* kg = k_pages + ((size_t)page * nkv + kvh) * PAGE * HD;
         const bf16* vg = v_pages + ((size_t)page * nkv + kvh) * PAGE * HD;
         bf16* ks = Ks + stage * PAGE * LD;

@@ -51,7 +51,7 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pages, 
         if (valid) {
             const int page = table[(size_t)seq * table_stride + j / page_size];
             if (page < 0 || page >= n_pages) {
-                if (status) atomicExch(status, 3);
+                ik_set_status(status, IK_STATUS_READ_NO_PAGE);
                 off = 0;
             } else {
                 off = (((size_t)page * nkv + kvh) * page_size + (j % page_size)) * hd;

@@ -111,6 +111,19 @@ __device__ __forceinline__ void ik_pdl_wait() { asm volatile("griddepcontrol.wai
 // it (not even a read-only one through `const __restrict__`) can be moved to before the wait.
 #define IK_AFTER_WAIT(ptr) asm volatile("" : "+l"(ptr))
 
+// The status word: kernels that meet something they refuse to do (an index out of range, a wait that ran out)
+// skip the access and set one bit per kind of event, so no cause hides another; the host reads and clears it.
+#define IK_STATUS_BAD_TOKEN 1            // a token id outside the vocabulary
+#define IK_STATUS_WRITE_NO_PAGE 2        // a cache write without a page
+#define IK_STATUS_READ_NO_PAGE 3         // a cache read without a page
+#define IK_STATUS_GEMM_TIMEOUT 4         // a tensor-core block that gave up waiting for its data
+#define IK_STATUS_SMEM_ALIGN 5           // shared memory not aligned for the tensor-core tiles
+#define IK_STATUS_BIT(code) (1 << ((code) - 1))
+__device__ __forceinline__ void ik_set_status(int* status, int code) { if (status) atomicOr(status, IK_STATUS_BIT(code)); }
+__device__ __forceinline__ bool ik_status_has(const int* status, int code) {
+    return status && (*(const volatile int*)status & IK_STATUS_BIT(code)) != 0;
+}
+
 // Streaming multiprocessors of the current device (asked once per device).  Grids of persistent kernels, split
 // choices and scratch sizes follow it.
 static inline int ik_sm_count() {

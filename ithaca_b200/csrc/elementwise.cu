@@ -16,7 +16,7 @@ __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < V;
-    if (!ok && threadIdx.x == 0 && status) atomicExch(status, 1);
+    if (!ok && threadIdx.x == 0) ik_set_status(status, IK_STATUS_BAD_TOKEN);
     const TW* row = table + (size_t)(ok ? id : 0) * d;
     float* o = out + (size_t)t * d;
     // this block's slice of the row (a few tokens would otherwise keep a few SMs busy), four elements a thread
@@ -206,7 +206,7 @@ rope_append_kernel(const float* __restrict__ qkv, TQ* __restrict__ q_out, TC* __
     if (write_cache && head_hi > nh) {
         const int page = table[(size_t)token_seq[t] * table_stride + pos / page_size];
         page_ok = page >= 0 && page < n_pages;
-        if (!page_ok) { if (tid == 0 && status) atomicExch(status, 2); }               // never write outside the pool
+        if (!page_ok) { if (tid == 0) ik_set_status(status, IK_STATUS_WRITE_NO_PAGE); }               // never write outside the pool
         else page_off = ((size_t)page * nkv * page_size + (pos % page_size)) * hd;
     }
     __syncthreads();

@@ -112,7 +112,8 @@ __device__ __forceinline__ float2 ld_cos_sin(const float2* p) {
 }
 
 // Waits until *flag is set by another block (acquire).  Bounded like mbar_wait.
-__device__ __forceinline__ bool flag_wait(const int* flag, volatile int* abort_flag, int* status) {
+__device__ __forceinline__ bool flag_wait(const int* flag, volatile int* abort_flag, int* status,
+                                          unsigned long long limit_ns = IK_WAIT_LIMIT_NS) {
     const unsigned long long t0 = globaltimer();
     for (int spin = 0;; spin++) {
         int v;
@@ -120,9 +121,9 @@ __device__ __forceinline__ bool flag_wait(const int* flag, volatile int* abort_f
         if (v) return true;
         if ((spin & 63) == 63) {
             if (*abort_flag) return false;
-            if (globaltimer() - t0 > 1000000000ull) {
+            if (globaltimer() - t0 > limit_ns) {
                 *abort_flag = 1;
-                if (status) atomicExch(status, IK_STATUS_GEMM_TIMEOUT);
+                ik_set_status(status, IK_STATUS_GEMM_TIMEOUT);
                 return false;
             }
         }
@@ -145,7 +146,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     typedef Cfg<BN> C;
     extern __shared__ unsigned char smem_raw[];
     __shared__ int rope_rows[4][BN];                   // per epilogue warp: the cache row of each of the tile's tokens
-    if (status && *(volatile int*)status == IK_STATUS_GEMM_TIMEOUT) return;     // an earlier block gave up
+    if (ik_status_has(status, IK_STATUS_GEMM_TIMEOUT)) return;     // an earlier block gave up
     unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = (uint64_t*)(tiles + C::STAGES * C::STAGE);
     uint64_t* empty = full + C::STAGES;
@@ -559,4 +560,48 @@ IK_EXPORT int ik_gemm_qkv_rope_tcgen05(const void* X, const void* W, float* part
                                        int splits, int* status, const IkRopeStore* rope, cudaStream_t stream) {
     if (!rope || !rope->q_out || (rope->hd & 1) || N != (rope->nh + 2 * rope->nkv) * rope->hd) return IK_BAD_ARGUMENT;
     return gemm_tcgen05_impl(X, W, nullptr, IK_F32, partial, M, N, K, ldx, ldw, N, 0, 0, splits, status, *rope, stream);
+}
+
+// ------------------------------------------------------------------------------------------
+// Self-test of the bounded waits: a wait that nothing will ever satisfy must give up after its limit, record
+// the event, raise the block's abort flag and let the kernel return; other waiting threads of the block must
+// then leave at once.  One block; thread 0 waits on an mbarrier nobody arrives at, thread 32 (after it) on the
+// same barrier with a long limit, thread 64 on a global flag that stays zero.
+// result: [0] thread 0's wait returned true?  [1] abort flag afterwards  [2] microseconds thread 0 waited
+//         [3] thread 32's wait returned true?  [4] microseconds it waited  [5] the flag wait returned true?
+namespace {
+__global__ void wait_expiry_kernel(int* status, int* result, const int* never_set, unsigned long long limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned long long t0 = globaltimer();
+        result[0] = mbar_wait(&bar, 0, &abort_flag, status, limit_ns) ? 1 : 0;
+        result[2] = (int)((globaltimer() - t0) / 1000);
+        result[1] = abort_flag;
+    }
+    __syncthreads();
+    if (threadIdx.x == 32) {
+        const unsigned long long t0 = globaltimer();
+        result[3] = mbar_wait(&bar, 0, &abort_flag, status, 200 * limit_ns) ? 1 : 0;
+        result[4] = (int)((globaltimer() - t0) / 1000);
+    }
+    if (threadIdx.x == 64) {
+        volatile int own_abort = 0;
+        result[5] = flag_wait(never_set, &own_abort, nullptr, limit_ns) ? 1 : 0;
+    }
+}
+}  // namespace
+
+// limit_ns is capped at 10 ms: the test is meant to run out quickly.
+IK_EXPORT int ik_selftest_wait_expires(int* status, int* result, const int* never_set, unsigned long long limit_ns,
+                                       cudaStream_t stream) {
+    if (!result || !never_set || limit_ns == 0 || limit_ns > 10000000ull) return IK_BAD_ARGUMENT;
+    wait_expiry_kernel<<<1, 96, 0, stream>>>(status, result, never_set, limit_ns);
+    IK_LAUNCH_STATUS();
 }

@@ -82,7 +82,9 @@ _SIGNATURES = {
     "ik_gemm_qkv_rope_mma": [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_gemm_qkv_rope_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
     "ik_attention_simt": [_vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp],
-    "ik_argmax": [_vp, _i, _vp, _i, _i, _vp],
+    "ik_argmax": [_vp, _i, _vp, _i, _i, _vp, _vp],
+    "ik_argmax_scratch_bytes": [],
+    "ik_selftest_wait_expires": [_vp, _vp, _vp, _u64, _vp],
     "ik_sample": [_vp, _i, _vp, _vp, _i, _i, _f, _i, _f, _f, _vp, _i, _u64, _vp, _vp, _vp],
 }
 
@@ -399,12 +401,43 @@ def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
     return out
 
 
-def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def selftest_wait_expires(status: torch.Tensor, limit_ns: int = 1_000_000) -> torch.Tensor:
+    """Runs the kernel library's check of its bounded waits: waits that nothing satisfies, with a limit of
+    ``limit_ns`` (at most 10 ms).  Returns int32 [6]: see gemm_tcgen05.cu."""
+    result = torch.full((6,), -1, dtype=torch.int32, device=status.device)
+    never = torch.zeros(1, dtype=torch.int32, device=status.device)
+    _check(lib().ik_selftest_wait_expires(_ptr(status), _ptr(result), _ptr(never), limit_ns, _stream()), "selftest_wait_expires")
+    return result
+
+
+_argmax_scratch = {}
+
+
+def argmax_scratch(device, fresh: bool = False) -> torch.Tensor:
+    """Scratch of the split argmax (counters and per-slice bests), zeroed once; the kernel leaves it as it found
+    it.  Launches that share one must follow one another in one stream: by default there is one per (device,
+    stream); ``fresh`` makes one for a caller that keeps its own (a captured graph)."""
+    if fresh:
+        return torch.zeros(lib().ik_argmax_scratch_bytes() // 4, dtype=torch.int32, device=device)
+    key = (str(torch.device(device)), _stream())
+    t = _argmax_scratch.get(key)
+    if t is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("argmax: no scratch exists for this stream yet and none can be made during a capture; "
+                              "pass one made with argmax_scratch(device, fresh=True)")
+        t = _argmax_scratch[key] = torch.zeros(lib().ik_argmax_scratch_bytes() // 4, dtype=torch.int32, device=device)
+    return t
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Index of each row's largest value (the lowest index among equals)."""
     _need(logits, "logits", torch.float32, contiguous=False)
     rows, V = logits.shape
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
-    _check(lib().ik_argmax(_ptr(logits), logits.stride(0), _ptr(out), rows, V, _stream()), "argmax")
+    if scratch is None:
+        scratch = argmax_scratch(logits.device)
+    _check(lib().ik_argmax(_ptr(logits), logits.stride(0), _ptr(out), rows, V, _ptr(scratch), _stream()), "argmax")
     return out
 
 

@@ -28,7 +28,7 @@ __device__ __forceinline__ int ik_rope_cache_row(const IkRopeStore& e, int m, in
     const int pos = e.token_pos[m];
     const int page = e.table[(size_t)e.token_seq[m] * e.table_stride + pos / e.page_size];
     if (page < 0 || page >= e.n_pages) {              // never write outside the pool
-        if (e.status) atomicExch(e.status, 2);
+        ik_set_status(e.status, IK_STATUS_WRITE_NO_PAGE);
         return -1;
     }
     return page * e.nkv * e.page_size + pos % e.page_size;
@@ -52,7 +52,7 @@ __device__ __forceinline__ void ik_rope_store_pair(const IkRopeStore& e, int m, 
     const int pos = e.token_pos[m];
     const int page = e.table[(size_t)e.token_seq[m] * e.table_stride + pos / e.page_size];
     if (page < 0 || page >= e.n_pages) {              // never write outside the pool
-        if (e.status) atomicExch(e.status, 2);
+        ik_set_status(e.status, IK_STATUS_WRITE_NO_PAGE);
         return;
     }
     const bool is_k = head < e.nh + e.nkv;

@@ -94,12 +94,15 @@ argmax_kernel(const float* __restrict__ logits, int ldl, int* __restrict__ out, 
 // The same with a row cut into ARG_SPLITS slices, one block each (a handful of rows would otherwise keep a
 // handful of SMs busy).  A slice's block leaves its best in scratch; the block that arrives last merges the
 // slices in slice order (so the result does not depend on which block that is) and clears the row's counter.
+// The scratch (a counter per row, then a best per row and slice) belongs to the caller: IK_ARGMAX_SCRATCH_BYTES,
+// zeroed once; every launch leaves the counters zero.  Launches that share a scratch must follow one another in
+// one stream, so a caller with several streams keeps one per stream.
 constexpr int ARG_SPLITS = 16, ARG_MAX_ROWS = 256;
-__device__ Best g_arg_part[ARG_MAX_ROWS * ARG_SPLITS];
-__device__ unsigned int g_arg_count[ARG_MAX_ROWS];
+constexpr size_t IK_ARGMAX_SCRATCH_BYTES = ARG_MAX_ROWS * sizeof(unsigned int) + (size_t)ARG_MAX_ROWS * ARG_SPLITS * sizeof(Best);
 
 __global__ void __launch_bounds__(ST)
-argmax_split_kernel(const float* __restrict__ logits, int ldl, int* __restrict__ out, int V) {
+argmax_split_kernel(const float* __restrict__ logits, int ldl, int* __restrict__ out, int V, unsigned int* g_arg_count) {
+    Best* const g_arg_part = reinterpret_cast<Best*>(g_arg_count + ARG_MAX_ROWS);
     ik_pdl_wait();
     ik_pdl_launch_dependents();
     __shared__ Best sh[32];
@@ -462,11 +465,16 @@ sample_kernel(const float* __restrict__ logits, int ldl, float* __restrict__ wor
 
 }  // namespace
 
-IK_EXPORT int ik_argmax(const float* logits, int ldl, int* out, int rows, int V, cudaStream_t stream) {
+IK_EXPORT int ik_argmax_scratch_bytes() { return (int)IK_ARGMAX_SCRATCH_BYTES; }
+
+// scratch: ik_argmax_scratch_bytes() of device memory, zeroed once by the caller and used by one stream at a time;
+// without it (null) every row is searched by one block.
+IK_EXPORT int ik_argmax(const float* logits, int ldl, int* out, int rows, int V, void* scratch, cudaStream_t stream) {
     if (rows < 0 || V <= 0 || ldl < V) return IK_BAD_ARGUMENT;
     if (rows == 0) return IK_OK;
-    if (rows <= ARG_MAX_ROWS && rows * ARG_SPLITS <= 1024 && V >= 16 * ST)
-        IK_RETURN_IF_ERROR(ik_launch(argmax_split_kernel, dim3(ARG_SPLITS, rows), ST, 0, stream, logits, ldl, out, V));
+    if (scratch && rows <= ARG_MAX_ROWS && rows * ARG_SPLITS <= 1024 && V >= 16 * ST)
+        IK_RETURN_IF_ERROR(ik_launch(argmax_split_kernel, dim3(ARG_SPLITS, rows), ST, 0, stream, logits, ldl, out, V,
+                                     (unsigned int*)scratch));
     else
         IK_RETURN_IF_ERROR(ik_launch(argmax_kernel, rows, ST, 0, stream, logits, ldl, out, V));
     IK_LAUNCH_STATUS();

@@ -5,7 +5,6 @@
 #include <cuda.h>
 #include "common.cuh"
 
-#define IK_STATUS_GEMM_TIMEOUT 4
 
 namespace {
 
@@ -32,18 +31,21 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Waits for the phase with the given parity to complete.  Gives up after ~1 s (or as soon as
-// another thread of the block has given up) and returns false.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+// Waits for the phase with the given parity to complete.  Gives up after `limit_ns` (about a second unless the
+// caller says otherwise), or as soon as another thread of the block has given up, and returns false; the thread
+// that gives up first raises the block's abort flag and records the event in the status word.
+constexpr unsigned long long IK_WAIT_LIMIT_NS = 1000000000ull;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                          unsigned long long limit_ns = IK_WAIT_LIMIT_NS) {
     if (mbar_test(bar, parity)) return true;
     const unsigned long long t0 = globaltimer();
     for (int spin = 0;; spin++) {
         if (mbar_test(bar, parity)) return true;
         if ((spin & 63) == 63) {
             if (*abort_flag) return false;
-            if (globaltimer() - t0 > 1000000000ull) {
+            if (globaltimer() - t0 > limit_ns) {
                 *abort_flag = 1;
-                if (status) atomicExch(status, IK_STATUS_GEMM_TIMEOUT);
+                ik_set_status(status, IK_STATUS_GEMM_TIMEOUT);
                 return false;
             }
         }

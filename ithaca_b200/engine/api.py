@@ -32,7 +32,7 @@ def _round_up(n: int, m: int) -> int:
 class Engine:
     def __init__(self, model_dir: Optional[str] = None, *, dtype: str = "bfloat16", device: str = "cuda:0",
                  max_tokens: Optional[int] = None, max_slots: Optional[int] = None, ctx: Optional[int] = None, graphs: bool = True,
-                 max_step_tokens: Optional[int] = 16384, _model=None, _config=None):
+                 max_step_tokens: Optional[int] = 16384, _model=None, _config=None, _source=None):
         """``max_tokens``: the most positions live sequences hold at any time, each rounded up
         to a multiple of 64; it sizes the cache (default: 8 sequences of ``ctx``).
         ``ctx``: the most positions one sequence may hold (default: the model's
@@ -49,7 +49,9 @@ class Engine:
             if model_dir is None:
                 raise ValueError("a model folder is needed")
             _model, _config = load_model(model_dir, self.runtime)
+            _source = ("folder", model_dir)
         self.model, self.config = _model, _config
+        self._source = _source
         spec = self.model.spec
         self.context_length = min(ctx, spec.max_position) if ctx else spec.max_position
         if max_tokens is None:
@@ -57,6 +59,9 @@ class Engine:
         self.cache = SequenceCache(self.model.cache_requests(), max_tokens=max_tokens, max_slots=max_slots,
                                    kv_dtype=self.runtime.kv_dtype, device=device)
         self.stepper = Stepper(self.model, self.cache, max_position=self.context_length, max_step_tokens=max_step_tokens)
+        self._status_host: Optional[torch.Tensor] = None
+        self._status_event: Optional[torch.cuda.Event] = None
+        self._status_pending = False
         self.last_stats: Optional[GenStats] = None
         self._sampler: Optional[Sampler] = None
         self._decoder = GraphDecoder(self.stepper) if graphs and getattr(self.model, "graph_safe", False) else None
@@ -64,17 +69,40 @@ class Engine:
     @classmethod
     def from_random(cls, config: Dict[str, Any], seed: int = 0, *, dtype: str = "bfloat16",
                     weights_dtype: Optional[str] = None, device: str = "cuda:0", **kw) -> "Engine":
-        """A model with random weights made on the device (nothing is written to disk)."""
+        """A model with random weights made on the device (nothing is written to disk).  The weights are
+        the ones ``write_random_model`` writes for the same configuration, seed and storage type."""
         if not torch.cuda.is_available():
             raise RuntimeError("ithaca_b200 runs on a CUDA device only; none is available")
         torch.cuda.set_device(device)
         arch, cfg = config_from_dict(config)
         runtime = Runtime(dtype=dtype, device=device)
-        tensors = random_tensors(weight_manifest(cfg.model_spec()), seed, weights_dtype or config.get("torch_dtype", "bfloat16"),
-                                 device=device)
+        manifest = weight_manifest(cfg.model_spec())
+        storage = weights_dtype or config.get("torch_dtype", "bfloat16")
+        tensors = random_tensors(manifest, seed, storage, device=device)
         model = build_model(arch, cfg, tensors, runtime)
-        eng = cls(None, dtype=dtype, device=device, _model=model, _config=cfg, **kw)
-        return eng
+        return cls(None, dtype=dtype, device=device, _model=model, _config=cfg,
+                   _source=("random", manifest, seed, storage), **kw)
+
+    def dump_tensor(self, name: str) -> torch.Tensor:
+        """The tensor of that name as the model was given it (host memory, storage type), before any part
+        stacked, reordered or converted it: from the folder the model was loaded from, or made again from
+        the seed.  For whoever wants to compute with the model's exact weights elsewhere."""
+        if self._source is None:
+            raise ValueError("this engine was built from a model object; it has no record of the tensors' origin")
+        if self._source[0] == "folder":
+            from ..weights.loader import read_model_tensors
+            found = read_model_tensors(self._source[1])
+            if name not in found:
+                raise KeyError(f"the model folder has no tensor '{name}'")
+            return found[name]
+        _, manifest, seed, storage = self._source
+        if name not in manifest:
+            raise KeyError(f"the model has no tensor '{name}'")
+        from ..weights.random_init import random_tensor
+        return random_tensor(name, manifest[name], seed, storage, "cpu")
+
+    def tensor_names(self) -> List[str]:
+        return sorted(weight_manifest(self.model.spec))
 
     # -- the step function ---------------------------------------------------------------------
     def _settle(self) -> None:
@@ -107,8 +135,46 @@ class Engine:
 
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
              want: Union[str, None, Sequence[Sequence[int]]] = "last") -> Optional[torch.Tensor]:
+        """Runs each slot's next tokens as one batch and returns float32 logits [wanted, vocab] on the
+        device.  The kernels' status word travels to the host behind the step without a wait; it is looked
+        at when the next call arrives (and by ``check_status``), so a refused access surfaces one call
+        later at the latest."""
         self._settle()
-        return self.stepper.step(slots, tokens, want)
+        self._poll_status()
+        logits = self.stepper.step(slots, tokens, want)
+        self._note_status()
+        return logits
+
+    def _note_status(self) -> None:
+        st = self.runtime.status
+        if st is None:
+            return
+        if self._status_host is None:
+            self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._status_event = torch.cuda.Event()
+        self._status_host.copy_(st, non_blocking=True)
+        self._status_event.record()
+        self._status_pending = True
+
+    def _poll_status(self, wait: bool = False) -> None:
+        if not self._status_pending:
+            return
+        if wait:
+            self._status_event.synchronize()
+        elif not self._status_event.query():
+            return
+        self._status_pending = False
+        word = int(self._status_host[0])
+        if word:
+            self.runtime.status.zero_()
+            from .step import describe_status
+            from ..cache.pages import CacheError
+            raise CacheError("a kernel reported " + describe_status(word) + "; the results since the last check are not to be used")
+
+    def check_status(self) -> None:
+        """Waits for the device and raises if a kernel has recorded something it refused to do."""
+        self._poll_status(wait=True)
+        self.stepper.check_status()
 
     # -- Backend of the generation loop --------------------------------------------------------
     def free_slots(self) -> int:

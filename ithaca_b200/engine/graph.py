@@ -48,6 +48,7 @@ class _Captured:
     logits: torch.Tensor
     out: torch.Tensor                    # device int32 [B + 1]: greedy ids, then the status word
     launches: int
+    pick_scratch: Optional[torch.Tensor] = None      # kept alive with the graph that writes it
     turn: int = 0
 
 
@@ -255,11 +256,12 @@ class GraphDecoder:
         torch.cuda.current_stream().synchronize()
         ctx.shared.clear()            # what the warm-up computed once per step has to be computed inside the graph too
         out = torch.empty(B + 1, dtype=torch.int32, device=st.runtime.device)
+        pick_scratch = ops.argmax_scratch(st.runtime.device, fresh=True)      # this graph's own: its replays follow one another
         graph = torch.cuda.CUDAGraph()
         n0 = ops.launch_count()
         with torch.cuda.graph(graph):
             logits = st.model.forward(ctx, st.cache)
-            ops.argmax(logits, out=out[:B])
+            ops.argmax(logits, out=out[:B], scratch=pick_scratch)
             out[B:].copy_(st.runtime.status)
         launches = ops.launch_count() - n0
         graph.replay()                                       # same tokens again: rewrites the same cache entries
@@ -269,7 +271,7 @@ class GraphDecoder:
             s.copy_(buffer)                                  # both start as the captured step's description
         torch.cuda.current_stream().synchronize()
         key = tuple(slots)
-        return _Captured(graph, buffer, offsets, sizes, stages, [None, None], [key, key], logits, out, launches)
+        return _Captured(graph, buffer, offsets, sizes, stages, [None, None], [key, key], logits, out, launches, pick_scratch)
 
     # -- used by the generation loop -------------------------------------------------------------
     def step_and_sample(self, slots, tokens, streams, counters, recent, sampler) -> List[int]:

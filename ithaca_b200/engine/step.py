@@ -154,16 +154,26 @@ class Stepper:
         return logits
 
     def check_status(self) -> None:
-        """Reads the flag that kernels set when they meet an index out of range (this
-        waits for the device).  The kernels skip such an access; the results of that step
-        are not to be used."""
+        """Reads the word in which kernels record what they refused to do (this waits for the
+        device) and clears it.  The kernels skip such an access; the results of the steps since
+        the last check are not to be used."""
         st = self.runtime.status
         if st is not None:
             v = int(st.item())
             if v != 0:
                 st.zero_()
-                what = {1: "a token id outside the vocabulary", 2: "a cache write without a page",
-                        3: "a cache read without a page",
-                        4: "a matrix-product block that gave up waiting for its data",
-                        5: "shared memory that is not aligned for the tensor-core tiles"}.get(v, f"code {v}")
-                raise CacheError(f"a kernel reported {what}")
+                raise CacheError("a kernel reported " + describe_status(v))
+
+
+STATUS_EVENTS = {1: "a token id outside the vocabulary", 2: "a cache write without a page",
+                 3: "a cache read without a page", 4: "a matrix-product block that gave up waiting for its data",
+                 5: "shared memory that is not aligned for the tensor-core tiles"}
+
+
+def describe_status(word: int) -> str:
+    """The status word holds one bit per kind of event (bit code - 1)."""
+    found = [what for code, what in STATUS_EVENTS.items() if word & (1 << (code - 1))]
+    rest = word & ~sum(1 << (c - 1) for c in STATUS_EVENTS)
+    if rest:
+        found.append(f"unknown bits {rest:#x}")
+    return "; ".join(found)

@@ -16,7 +16,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 # random through the layers: a few 1e-3 of the logit scale; 2e-2 bounds the worst of thousands of logits.
 REL = {"float32": 2e-5, "bfloat16": 2e-2}
 # The same engine under different cuttings of the same tokens.
-REL_CUT = {"float32": 2e-6, "bfloat16": 1e-2}
+# float32: none at all.  Every sum of that path runs in an order that depends on the position and size of what is
+# summed only, never on the step's shape, so two cuttings of the same tokens must give the same bits.
+REL_CUT = {"float32": 0.0, "bfloat16": 1e-2}
 
 
 def rel_err(got: np.ndarray, ref: np.ndarray) -> float:
@@ -70,3 +72,36 @@ def run_trace(model_dir, dtype, out_dir, max_tokens, steps, timeout=900):
         else:
             assert not os.path.exists(path)
     return out
+
+
+def run_schedule(eng, requests, schedule, truncations=None):
+    """Feeds ``requests`` (lists of token ids) through ``eng.step`` as ``schedule`` says: a list of steps, each a
+    list of (request, n) = request brings its next n tokens.  ``truncations``: {step index: [(request, keep)]}, done
+    before that step; the request's next tokens then follow position ``keep`` (its tokens from there on are fed
+    again).  A request gets its slot when it first appears and gives it back after its last token.  Returns the
+    logits of every (request, position) as float32 arrays [len(request), vocab] (the last feeding of a position
+    counts)."""
+    slots, fed, got = {}, {}, {}
+    for n, step in enumerate(schedule):
+        for r, keep in (truncations or {}).get(n, []):
+            eng.truncate(slots[r], keep)
+            fed[r] = keep
+        for r, _ in step:
+            if r not in slots:
+                slots[r] = eng.alloc_slot()
+                fed[r] = 0
+        toks = [requests[r][fed[r]:fed[r] + k] for r, k in step]
+        assert all(len(t) == k for t, (_, k) in zip(toks, step)), "the schedule feeds more tokens than a request has"
+        lg = eng.step([slots[r] for r, _ in step], toks, "all").cpu().numpy()
+        off = 0
+        for r, k in step:
+            if r not in got:
+                got[r] = np.zeros((len(requests[r]), lg.shape[1]), dtype=np.float32)
+            got[r][fed[r]:fed[r] + k] = lg[off:off + k]
+            off += k
+            fed[r] += k
+            if fed[r] == len(requests[r]) and not any(r == q for later in schedule[n + 1:] for q, _ in later):
+                eng.free_slot(slots.pop(r))
+    eng.check_status()
+    assert not slots, "the schedule leaves requests unfinished"
+    return got

@@ -520,3 +520,26 @@ def test_sample_follows_the_distribution():
     p = torch.softmax(lg[0][top].double(), 0)
     freq = torch.tensor([(got == i).sum().item() for i in top], dtype=torch.double) / n
     assert (freq - p).abs().max().item() < 4 * math.sqrt(0.25 / n)
+
+
+def test_a_wait_that_nothing_satisfies_gives_up_and_returns():
+    """The tensor-core kernels wait on barriers and flags with a limit.  Here the limit is 1 ms and nothing ever
+    arrives: the wait returns false after about that long, the event is recorded in the status word (bit of
+    code 4), the block's abort flag is up, a second waiter of the block leaves at once although its own limit is
+    far away, the wait on a global flag runs out the same way, and the device goes on working afterwards."""
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    res = ops().selftest_wait_expires(status, limit_ns=1_000_000).cpu().tolist()
+    assert res[0] == 0 and res[1] == 1, res                  # gave up; abort flag raised
+    assert 900 <= res[2] <= 20000, res                       # after about a millisecond
+    assert res[3] == 0 and res[4] < 500, res                 # the second waiter saw the flag, not its 200 ms
+    assert res[5] == 0, res                                  # the flag wait of the stream-K pieces, too
+    assert status.item() == 1 << 3
+    # a product given that status word returns at once and leaves its output alone; with a clean word it computes
+    x, w = rnd((40, 256), 1, torch.bfloat16).to(DEV), rnd((256, 256), 2, torch.bfloat16).to(DEV)
+    out = torch.full((40, 256), 7.0, device=DEV)
+    ops().gemm_tcgen05(x, w, out=out, status=status, splits=1)
+    assert float(out.min()) == 7.0 and float(out.max()) == 7.0
+    status.zero_()
+    ops().gemm_tcgen05(x, w, out=out, status=status, splits=1)
+    close(out, x.double().cpu() @ w.double().cpu().T, 2e-5)
+    assert status.item() == 0

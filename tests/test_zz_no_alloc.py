@@ -60,6 +60,24 @@ def test_static_scratch_gives_the_same_ids_twice_in_a_row():
         assert got.cpu().tolist() == want.cpu().tolist()
 
 
+def test_the_static_entry_point_takes_no_device_memory():
+    """What the entry point is for: between a warmed-up state and the end of a call neither the driver's count of
+    free device memory nor torch's own allocator has moved."""
+    fn, ops = static_entry()
+    logits, recent, streams, counters = case(8, 5003, 7)
+    st, _ = call_static(fn, logits, 0.8, 40, 0.9, 1.1, recent, 99, streams, counters)     # first call on the device: set-up
+    assert st == 0
+    torch.cuda.synchronize()
+    out = torch.empty(8, dtype=torch.int32, device=DEV)
+    free0, held0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+    for _ in range(3):
+        st = fn(logits.data_ptr(), logits.stride(0), out.data_ptr(), 8, 5003, 0.8, 40, 0.9, 1.1, recent.data_ptr(), 64, 99,
+                streams.data_ptr(), counters.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert st == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0 and torch.cuda.memory_allocated() == held0
+
+
 def test_a_request_beyond_the_static_array_is_refused(capfd):
     fn, _ = static_entry()
     rows, V = 17, 128256                                 # 2,180,352 floats > 2,097,152
