@@ -2,6 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl reference]
     python bench.py --only decode|prefill|attention|products   one part alone (small cases for profiling)
+    python bench.py --config 1b-unequal|13b-long                the other two workloads alone, through Engine.generate
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at the given batch with every
 sequence's cache filled to the context length; a step is one decode step (forward pass of one
@@ -12,6 +13,11 @@ upload of the step's description and one read-back of the sampled ids per step).
 short pause and held against the burst peak; back to back the step takes about a tenth longer
 under the power cap).  ``roofline`` divides the bytes a decode step
 has to read (every weight once, and the cache of the live sequences) by its time.
+``points`` holds decoding at batch 1 and 64 and the two other workloads, each through ``Engine.generate``:
+``1b_unequal`` (Llama-3.2-1B shape, 64 prompts of 16 to 2,048 tokens in one prompt step, then 256 decode steps) and
+``13b_long`` (Llama-2-13B shape, 8 prompts of 1,024 tokens decoded to 4,096 positions, with the rate near 1,024,
+2,048 and 4,096).  Peaks come from MEASURED_PEAKS.json; when that file is absent they are measured here with
+this library's own copy and tcgen05 product kernels.
 Weights are random (seeded), token ids are seeded-uniform: no dataset, no checkpoint.
 """
 import argparse
@@ -49,26 +55,24 @@ SHAPES = {"8b": ("Llama-3.1-8B shape", LLAMA_3_1_8B), "1b": ("Llama-3.2-1B shape
           "13b": ("Llama-2-13B shape", LLAMA_2_13B)}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+E2E_STEPS = 128
 
 
 def peaks():
+    """The roofline's denominators: the driver's measurement if its file is there, else measured now with this
+    library's own kernels (the reference measures its device the same way, src/hub.cpp:503-549)."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.isfile(path):
         try:
             with open(path) as f:
                 d = json.load(f)
-            out = dict(FALLBACK_PEAKS)
-            for k in out:
-                if isinstance(d.get(k), (int, float)):
-                    out[k] = float(d[k])
-            out["source"] = "measured"
-            return out
+            if all(isinstance(d.get(k), (int, float)) for k in ("hbm_gbs", "bf16_tflops")):
+                return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
         except (OSError, ValueError):
             pass
-    out = dict(FALLBACK_PEAKS)
-    out["source"] = "fallback"
-    return out
+    from ithaca_b200.engine.profile import measure_peaks
+    out = measure_peaks("cuda:0")
+    return {"hbm_gbs": out["hbm_gbs"], "bf16_tflops": out["bf16_tflops"], "source": "self-measured"}
 
 
 class ClockSampler:
@@ -153,17 +157,107 @@ def decode_run(eng, batch, steps, warmup, vocab, context, clocks=None):
 
 
 def e2e_run(eng, batch, steps, vocab, context):
-    """The same decode steps through the public entry point: host ids in, host ids out."""
+    """The same decode steps through the public entry point: host ids in, host ids out.  Always over the same
+    number of steps, whatever --steps says.  The steps right behind the long prompt step run slower (the device
+    comes out of the prompt's power draw), so the rate of the first 32 steps is given beside the settled one."""
     import numpy as np
     rng = np.random.default_rng(77)
     prompts = [rng.integers(0, vocab, size=context - steps - 1).tolist() for _ in range(batch)]
     # warm-up over the same lengths: every graph shape the timed run meets exists afterwards
     eng.generate(prompts, max_tokens=steps + 1, temp=0.0, rep_pen=1.0, stop_token_ids=[])
-    out = eng.generate(prompts, max_tokens=steps + 1, temp=0.0, rep_pen=1.0, stop_token_ids=[])
+    stamps = []
+
+    def on_token(request, token):
+        if request == 0:
+            stamps.append(time.perf_counter())
+        return True
+
+    out = eng.generate(prompts, max_tokens=steps + 1, temp=0.0, rep_pen=1.0, stop_token_ids=[], on_token=on_token)
     st = eng.last_stats
-    assert all(len(o) == steps + 1 for o in out)
+    assert all(len(o) == steps + 1 for o in out) and len(stamps) == steps + 1
     # the first token of each sequence comes from the prefill step; the decode clock covers the rest
-    return {"tok_s": batch * steps / st.decode_seconds, "h2d": eng._decoder.last_upload_bytes, "d2h": batch * 4 + 4}
+    return {"tok_s": batch * steps / st.decode_seconds, "h2d": eng._decoder.last_upload_bytes, "d2h": batch * 4 + 4,
+            "first32_tok_s": batch * 32 / (stamps[32] - stamps[0]),
+            "settled_tok_s": batch * (steps - 64) / (stamps[steps] - stamps[64]), "steps": steps}
+
+
+def unequal_1b_run(pk):
+    """Llama-3.2-1B shape: 64 prompts with lengths uniform in 16..2,048 as one prompt step (which the engine runs in
+    passes of at most 16,384 tokens), then 256 decode steps, through Engine.generate."""
+    import numpy as np
+    import torch
+    from ithaca_b200 import Engine
+    name, cfg = SHAPES["1b"]
+    n_req, steps = 64, 256
+    rng = np.random.default_rng(4)
+    lens = [int(x) for x in rng.integers(16, 2049, size=n_req)]
+    vocab = cfg["vocab_size"]
+    prompts = [rng.integers(0, vocab, size=n).tolist() for n in lens]
+    room = sum(-(-(n + steps + 1) // 64) * 64 for n in lens)
+    eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=room, max_slots=n_req, ctx=2048 + steps + 64)
+    opts = dict(max_tokens=steps + 1, temp=0.0, rep_pen=1.0, stop_token_ids=[])
+    eng.generate(prompts, **opts)                         # warm-up: the same lengths, so every graph shape exists
+    torch.cuda.synchronize()
+    out = eng.generate(prompts, **opts)
+    st = eng.last_stats
+    assert all(len(o) == steps + 1 for o in out) and st.batches == 1
+    mean_kv = sum(lens) / n_req + steps / 2
+    step_bytes = eng.model.weight_bytes() + eng.cache.bytes_per_token() * mean_kv * n_req
+    gbs = step_bytes / (st.decode_seconds / steps) / 1e9
+    layer_flops, head_flops = model_flops_per_token(cfg, cfg["num_hidden_layers"])
+    attn = sum(4 * cfg["num_attention_heads"] * cfg["head_dim"] * n * (n + 1) / 2 for n in lens) * cfg["num_hidden_layers"]
+    pre_flops = layer_flops * sum(lens) + attn + head_flops * n_req
+    res = {"model": name, "requests": n_req, "prompt_tokens": sum(lens), "prompt_passes": eng.stepper.max_step_tokens,
+           "prefill_tok_s": round(sum(lens) / st.prefill_seconds, 1),
+           "prefill_frac": round(pre_flops / st.prefill_seconds / (pk["bf16_tflops"] * 1e12), 4),
+           "decode_steps": steps, "decode_tok_s": round(n_req * steps / st.decode_seconds, 1),
+           "mean_kv_len": round(mean_kv, 1), "step_gb": round(step_bytes / 1e9, 3), "hbm_frac": round(gbs / pk["hbm_gbs"], 4)}
+    del eng
+    torch.cuda.empty_cache()
+    return res
+
+
+def long_13b_run(pk):
+    """Llama-2-13B shape: 8 prompts of 1,024 tokens, decoded until every sequence holds 4,096 positions, through
+    Engine.generate; the rate is taken over 128 steps near 1,024, 2,048 and 4,096 positions from the host's clock
+    at each token."""
+    import numpy as np
+    import torch
+    from ithaca_b200 import Engine
+    name, cfg = SHAPES["13b"]
+    batch, prompt_len, final = 8, 1024, 4096
+    steps = final - prompt_len
+    vocab = cfg["vocab_size"]
+    rng = np.random.default_rng(6)
+    eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=batch * (final + 64), max_slots=batch, ctx=final + 64)
+    opts = dict(temp=0.0, rep_pen=1.0, stop_token_ids=[])
+    # warm-up: a short run at each width of block table the long run will meet (16 to 32, and 33 to 64 pages)
+    for n in (prompt_len, 2048 + 8):
+        eng.generate([rng.integers(0, vocab, size=n).tolist() for _ in range(batch)], max_tokens=4, **opts)
+    prompts = [rng.integers(0, vocab, size=prompt_len).tolist() for _ in range(batch)]
+    stamps = []
+
+    def on_token(request, token):
+        if request == 0:
+            stamps.append(time.perf_counter())
+        return True
+
+    torch.cuda.synchronize()
+    out = eng.generate(prompts, max_tokens=steps + 1, on_token=on_token, **opts)
+    st = eng.last_stats
+    assert all(len(o) == steps + 1 for o in out) and len(stamps) == steps + 1
+    weight_bytes, per_token = eng.model.weight_bytes(), eng.cache.bytes_per_token()
+    res = {"model": name, "batch": batch, "prompt_len": prompt_len, "final_len": final,
+           "prefill_tok_s": round(batch * prompt_len / st.prefill_seconds, 1),
+           "decode_tok_s": round(batch * steps / st.decode_seconds, 1)}
+    for label, s0 in (("1024", 0), ("2048", 2048 - prompt_len - 64), ("4096", steps - 128)):
+        dt = (stamps[s0 + 128] - stamps[s0]) / 128
+        kv = prompt_len + s0 + 64
+        res[f"tok_s_at_{label}"] = round(batch / dt, 1)
+        res[f"hbm_frac_at_{label}"] = round((weight_bytes + per_token * kv * batch) / dt / 1e9 / pk["hbm_gbs"], 4)
+    del eng
+    torch.cuda.empty_cache()
+    return res
 
 
 def prefill_run(eng, tokens, vocab, reps=5):
@@ -281,7 +375,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES),
                     help="layer sizes: 8b is the benchmark's configuration, the others are for comparison")
-    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points and the two other workloads")
+    ap.add_argument("--config", default=None, choices=["1b-unequal", "13b-long"],
+                    help="run one of the other workloads alone and print its figures")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention", "products"],
                     help="run one part only and print its figures (for profiling a small case)")
     args = ap.parse_args()
@@ -300,6 +396,10 @@ def main():
     from ithaca_b200 import Engine
 
     pk = peaks()
+    if args.config:
+        res = unequal_1b_run(pk) if args.config == "1b-unequal" else long_13b_run(pk)
+        print(json.dumps({"config": args.config, "peaks": pk["source"], **res}))
+        return 0
     shape_name, shape_cfg = SHAPES[args.shape]
     cfg = dict(shape_cfg)
     if args.only == "products":
@@ -336,7 +436,7 @@ def main():
     if point_batches:
         for b in point_batches:
             points[f"decode_b{b}"] = round(decode_run(eng, b, min(args.steps, 32), args.warmup, vocab, CONTEXT)["tok_s"], 1)
-    e2e = e2e_run(eng, args.batch, args.steps, vocab, CONTEXT)
+    e2e = e2e_run(eng, args.batch, E2E_STEPS, vocab, CONTEXT)
     pre_ms = prefill_run(eng, PREFILL_TOKENS, vocab)
 
     layer_flops, head_flops = model_flops_per_token(cfg, n_layers)
@@ -358,7 +458,8 @@ def main():
                    "cache_page": 64, "peaks": pk["source"]},
         "clocks": main_run["clocks"],
         "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tok/s", "h2d_bytes_per_step": e2e["h2d"],
-                "d2h_bytes_per_step": e2e["d2h"]},
+                "d2h_bytes_per_step": e2e["d2h"], "steps": e2e["steps"], "first32_tok_s": round(e2e["first32_tok_s"], 1),
+                "settled_tok_s": round(e2e["settled_tok_s"], 1)},
         "gpu_launches": main_run["launches_per_step"] * args.steps,
         "prefill": {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
                     "frac": round(pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
@@ -366,6 +467,11 @@ def main():
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
     }
+    if not args.no_points and args.shape == "8b" and not args.layers:
+        del eng
+        torch.cuda.empty_cache()
+        points["1b_unequal"] = unequal_1b_run(pk)
+        points["13b_long"] = long_13b_run(pk)
     print(json.dumps(line))
     return 0
 

@@ -335,7 +335,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int i = 0; i <= n_iter; i++) {
                 if (i < n_iter) {
                     const int s = i % TC_NS;
-                    if (!mbar_wait(k_free + s, ((i / TC_NS) & 1) ^ 1, abort_flag, status)) break;
+                    if (!mbar_wait(k_free + s, ((i / TC_NS) & 1) ^ 1, abort_flag, status, IK_WAIT_LIMIT_NS, 11, i)) break;
                     const int row = page_row(i);
                     mbar_expect_tx(k_full + s, TC_KV_BYTES);
                     for (int bx = 0; bx < TC_BOXES; bx++)
@@ -343,7 +343,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
                 if (i > 0) {
                     const int s = (i - 1) % TC_NS;
-                    if (!mbar_wait(v_free + s, (((i - 1) / TC_NS) & 1) ^ 1, abort_flag, status)) break;
+                    if (!mbar_wait(v_free + s, (((i - 1) / TC_NS) & 1) ^ 1, abort_flag, status, IK_WAIT_LIMIT_NS, 12, i)) break;
                     const int row = page_row(i - 1);
                     mbar_expect_tx(v_full + s, TC_KV_BYTES);
                     for (int bx = 0; bx < TC_BOXES; bx++)
@@ -355,10 +355,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (lane == 0) {
             const uint32_t idesc_qk = umma_idesc(PAGE), idesc_pv = umma_idesc(HD, 1);
             const uint32_t q_addr = smem_u32(Qs);
-            bool ok = mbar_wait(q_full, 0, abort_flag, status);
+            bool ok = mbar_wait(q_full, 0, abort_flag, status, IK_WAIT_LIMIT_NS, 13, 0);
             auto issue_qk = [&](int i) -> bool {
                 const int s = i % TC_NS;
-                if (!mbar_wait(k_full + s, (i / TC_NS) & 1, abort_flag, status)) return false;
+                if (!mbar_wait(k_full + s, (i / TC_NS) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 14, i)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t k_addr = smem_u32(Ks + s * TC_KV_BYTES);
                 #pragma unroll
@@ -373,7 +373,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int i = 0; i < n_iter && ok; i++) {
                 if (i + 1 < n_iter) { ok = issue_qk(i + 1); if (!ok) break; }     // runs while page i is in the softmax
                 const int s = i % TC_NS;
-                ok = mbar_wait(p_ready, i & 1, abort_flag, status) && mbar_wait(v_full + s, (i / TC_NS) & 1, abort_flag, status);
+                ok = mbar_wait(p_ready, i & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 15, i) && mbar_wait(v_full + s, (i / TC_NS) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 16, i);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t v_addr = smem_u32(Vs + s * TC_KV_BYTES);
@@ -394,7 +394,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         bool ok = true;
         for (int i = 0; i < n_iter && ok; i++) {
             const int p = p_lo + i;
-            ok = mbar_wait(s_full + (i & 1), (i >> 1) & 1, abort_flag, status);
+            ok = mbar_wait(s_full + (i & 1), (i >> 1) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 17, i);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float sc[PAGE];
@@ -444,7 +444,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 // O is at rest between the product of the page before (waited for here) and this page's (which waits
                 // for this thread).  The barrier has completed i - 1 or i phases at this point, whatever was waited
                 // for earlier, so the parity names the right one.
-                ok = mbar_wait(pv_done, (i - 1) & 1, abort_flag, status);
+                ok = mbar_wait(pv_done, (i - 1) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 18, i);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 #pragma unroll
@@ -473,7 +473,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // (The scores of page i + 1 can be there before that, so a thread that is ahead would otherwise complete
             // the phase of one that is behind, and the product would read probabilities not yet written.)
             if (i > 0) {
-                ok = mbar_wait(p_ready, (i - 1) & 1, abort_flag, status);
+                ok = mbar_wait(p_ready, (i - 1) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 19, i);
                 if (!ok) break;
             }
             mbar_arrive(p_ready);
@@ -481,8 +481,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // The last product.  Nothing above has waited for the one before it (it is known to have run only up to two
         // pages back: the scores of the last page were there), and a parity names a phase only if the phase before
         // it is over: so that one is waited for first.
-        if (ok && n_iter > 1) ok = mbar_wait(pv_done, (n_iter - 2) & 1, abort_flag, status);
-        if (ok && mbar_wait(pv_done, (n_iter - 1) & 1, abort_flag, status)) {
+        if (ok && n_iter > 1) ok = mbar_wait(pv_done, (n_iter - 2) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 20, n_iter);
+        if (ok && mbar_wait(pv_done, (n_iter - 1) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 21, n_iter)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = 1.0f / l;
             bf16* orow = out + ((size_t)(q_begin + row0 + r) * nh + h) * HD;
@@ -721,6 +721,11 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
 }  // namespace
 
 IK_EXPORT int ik_attn_head_dim() { return HD; }
+
+// Sites of the tcgen05 prefill kernel's waits: 11, 12 = loader for a free key / value stage; 13 = issuer for the
+// queries; 14 = issuer for keys; 15 = issuer for the probabilities; 16 = issuer for values; 17 = softmax for scores;
+// 18 = softmax for the product before a rescaling; 19 = softmax for the others' arrivals; 20, 21 = the last products.
+IK_EXPORT int ik_attn_take_wait_record(int* out4) { return ik_take_wait_record(out4); }
 
 IK_EXPORT int ik_attn_prefill(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_seqlens,
                               const int* kv_lens, const int* table, int table_stride, int B, int max_new, int nh,

@@ -12,6 +12,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from . import build
+from . import ops
 from .ops import KernelError, _check, _ptr, _stream, sm_count
 
 _vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
@@ -57,16 +58,18 @@ def module(head_dim: int) -> ctypes.CDLL:
         m.ik_attn_decode.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _i, _i, _i, _i,
                                      _vp, _vp]
         m.ik_attn_decode.restype = _i
+        m.ik_attn_take_wait_record.argtypes = [_vp]
+        m.ik_attn_take_wait_record.restype = _i
         if m.ik_attn_head_dim() != head_dim:
             raise KernelError("the attention module was compiled for another head size")
         _modules[key] = m
-    return m
+    return ops.timed(m)
 
 
 def prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, cu_seqlens: torch.Tensor,
             kv_lens: torch.Tensor, table: torch.Tensor, n_seqs: int, max_new: int, n_heads: int, scale: float,
             window: int, status: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
-            kind: str = "auto") -> torch.Tensor:
+            kind: str = "auto", work: Optional[Tuple[int, int]] = None) -> torch.Tensor:
     """``kind``: "tc" = the tcgen05 kernel (head sizes 64 and 128), "mma" = the warp-level kernel,
     "auto" = tcgen05 where it applies."""
     n_pages, nkv, page_size, hd = k_pages.shape
@@ -74,6 +77,7 @@ def prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, cu_se
     if out is None:
         out = torch.empty_like(q)
     if kind == "tc" or (kind == "auto" and hd in (64, 128)):
+        ops._work(f"attention prefill tcgen05 {q.shape[0]}x{n_heads}", *(work or (0, 0)))
         st = m.ik_attn_prefill_tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(cu_seqlens), _ptr(kv_lens),
                                   _ptr(table), table.stride(0), q.shape[0], n_seqs, max_new, n_heads, nkv, scale, window,
                                   page_size, n_pages, _ptr(status), _stream())
@@ -82,6 +86,7 @@ def prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, cu_se
             return out
         if kind == "tc":
             raise KernelError("attention prefill (tcgen05): head size or alignment not supported")
+    ops._work(f"attention prefill mma {q.shape[0]}x{n_heads}", *(work or (0, 0)))
     _check(m.ik_attn_prefill(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(cu_seqlens), _ptr(kv_lens),
                              _ptr(table), table.stride(0), n_seqs, max_new, n_heads, nkv, scale, window, page_size,
                              n_pages, _ptr(status), _stream()), "attention prefill")
@@ -90,7 +95,8 @@ def prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, cu_se
 
 def decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, kv_lens: torch.Tensor, table: torch.Tensor,
            n_seqs: int, kv_len_bound: int, n_heads: int, scale: float, window: int, status: Optional[torch.Tensor],
-           out: Optional[torch.Tensor] = None, chunk_pages: int = DECODE_CHUNK_PAGES, ring_kb: int = 0) -> torch.Tensor:
+           out: Optional[torch.Tensor] = None, chunk_pages: int = DECODE_CHUNK_PAGES, ring_kb: int = 0,
+           work: Optional[Tuple[int, int]] = None) -> torch.Tensor:
     """``kv_len_bound``: no sequence of the step is longer than this (it sizes the grid and the
     scratch for the partial results; blocks beyond a sequence's length return at once)."""
     n_pages, nkv, page_size, hd = k_pages.shape
@@ -100,6 +106,7 @@ def decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, kv_len
     part_ml = torch.empty((n_seqs, n_heads, n_splits, 2), dtype=torch.float32, device=q.device)
     if out is None:
         out = torch.empty_like(q)
+    ops._work(f"attention decode {n_seqs}x{n_heads}", *(work or (0, 0)))
     _check(m.ik_attn_decode(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(part_o), _ptr(part_ml),
                             _ptr(kv_lens), _ptr(table), table.stride(0), n_seqs, n_heads, nkv, scale, window,
                             page_size, n_pages, chunk_pages, n_splits, ring_kb, _ptr(status), _stream()), "attention decode", kernels=2)
@@ -113,9 +120,18 @@ def attend(q, k_pages, v_pages, ctx, table, n_heads: int, scale: float, window: 
     n_pages, nkv, page_size, hd = k_pages.shape
     if k_pages.dtype != torch.bfloat16 or q.dtype != torch.bfloat16 or page_size != 64 or not supported(hd):
         return None
+    work = None
+    if ops.profiling():
+        # (query, key) pairs under the causal mask (and the window), from the host's copy of the lengths
+        pairs = 0
+        for n, end in zip(ctx.host_n_new, ctx.host_kv_lens):
+            for p in range(end - n, end):
+                pairs += min(p + 1, window) if window else p + 1
+        keys = sum(min(e, window + n) if window else e for n, e in zip(ctx.host_n_new, ctx.host_kv_lens))
+        work = (2 * q.numel() * 2 + 2 * keys * nkv * hd * 2, 4 * hd * n_heads * pairs)
     if ctx.is_decode:
         chunk = decode_chunk_pages(ctx.n_seqs, n_heads, nkv, ctx.max_kv_len, page_size)
         return decode(q, k_pages, v_pages, ctx.kv_lens, table, ctx.n_seqs, ctx.kv_len_bound, n_heads, scale, window,
-                      status, chunk_pages=chunk)
+                      status, chunk_pages=chunk, work=work)
     return prefill(q, k_pages, v_pages, ctx.cu_seqlens, ctx.kv_lens, table, ctx.n_seqs, ctx.max_new, n_heads, scale,
-                   window, status)
+                   window, status, work=work)

@@ -114,14 +114,15 @@ __device__ __forceinline__ float2 ld_cos_sin(const float2* p) {
 // Waits until *flag is set by another block (acquire).  Bounded like mbar_wait.
 __device__ __forceinline__ bool flag_wait(const int* flag, volatile int* abort_flag, int* status,
                                           unsigned long long limit_ns = IK_WAIT_LIMIT_NS) {
-    const unsigned long long t0 = globaltimer();
+    const long long c0 = wait_clock();
     for (int spin = 0;; spin++) {
         int v;
         asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
         if (v) return true;
         if ((spin & 63) == 63) {
             if (*abort_flag) return false;
-            if (globaltimer() - t0 > limit_ns) {
+            if (wait_ran_out(c0, limit_ns)) {
+                note_wait_gave_up(5, (int)(flag - (const int*)nullptr) & 0xFFFF, 0);
                 *abort_flag = 1;
                 ik_set_status(status, IK_STATUS_GEMM_TIMEOUT);
                 return false;
@@ -206,7 +207,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     const int s = it % C::STAGES;
                     unsigned char* a = tiles + s * C::STAGE;
                     if (it >= pre_issued) {             // the first stages are armed and their weights asked for already
-                        if (!mbar_wait(empty + s, ((it / C::STAGES) & 1) ^ 1, abort_flag, status)) { ok = false; break; }
+                        if (!mbar_wait(empty + s, ((it / C::STAGES) & 1) ^ 1, abort_flag, status, IK_WAIT_LIMIT_NS, 1, it)) { ok = false; break; }
                         mbar_expect_tx(full + s, C::STAGE);
                         tma_load_2d(a, &map_w, (kb0 + i) * BK, n0, full + s);
                     }
@@ -217,8 +218,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (*abort_flag) {
                 // leave no copy of this block in flight: wait (bounded) for the stages that were armed last
                 for (int i = max(0, armed - C::STAGES); i < armed; i++) {
-                    const unsigned long long t0 = globaltimer();
-                    while (!mbar_test(full + i % C::STAGES, (i / C::STAGES) & 1) && globaltimer() - t0 < 2000000ull) {}
+                    const long long c0 = wait_clock();
+                    while (!mbar_test(full + i % C::STAGES, (i / C::STAGES) & 1) && !wait_ran_out(c0, 2000000ull)) {}
                 }
             }
         }
@@ -231,13 +232,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             for (Work w; ok && walk.next(w); lt++) {
                 const int nkb = w.nkb;
                 const int buf = lt & 1;
-                ok = mbar_wait(acc_empty + buf, ((lt >> 1) & 1) ^ 1, abort_flag, status);   // drained by the epilogue
+                ok = mbar_wait(acc_empty + buf, ((lt >> 1) & 1) ^ 1, abort_flag, status, IK_WAIT_LIMIT_NS, 2, lt);   // drained by the epilogue
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem_base + buf * C::ACC_COLS;
                 for (int i = 0; i < nkb; i++, it++) {
                     const int s = it % C::STAGES;
-                    ok = mbar_wait(full + s, (it / C::STAGES) & 1, abort_flag, status);
+                    ok = mbar_wait(full + s, (it / C::STAGES) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 3, it);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t a = smem_u32(tiles + s * C::STAGE), b = a + C::A_BYTES;
@@ -291,7 +292,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 fetch_piece(c_lo, 0, ahead[0]);
                 fetch_piece(c_lo + 1, 0, ahead[1]);
             }
-            if (!mbar_wait(acc_full + buf, (lt >> 1) & 1, abort_flag, status)) break;
+            if (!mbar_wait(acc_full + buf, (lt >> 1) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 4, lt)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * C::ACC_COLS;
             if (hand_over) {
@@ -597,6 +598,10 @@ __global__ void wait_expiry_kernel(int* status, int* result, const int* never_se
     }
 }
 }  // namespace
+
+// Sites of the product's waits: 1 = loader for a free stage, 2 = MMA issuer for a drained accumulator, 3 = MMA issuer
+// for a loaded stage, 4 = epilogue for a finished accumulator, 5 = stream-K gather for another block's piece; 99 = self-test.
+IK_EXPORT int ik_gemm_tcgen05_take_wait_record(int* out4) { return ik_take_wait_record(out4); }
 
 // limit_ns is capped at 10 ms: the test is meant to run out quickly.
 IK_EXPORT int ik_selftest_wait_expires(int* status, int* result, const int* never_set, unsigned long long limit_ns,

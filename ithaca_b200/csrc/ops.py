@@ -72,6 +72,7 @@ _SIGNATURES = {
     "ik_swiglu": [_vp, _vp, _i, _i, _i, _i, _vp],
     "ik_fill_random": [_vp, _i, _u64, _u64, _f, _f, _vp],
     "ik_device_sm_count": [],
+    "ik_copy": [_vp, _vp, _u64, _vp],
     "ik_rope_append": [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "ik_gemm_bf16_mma": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
@@ -85,11 +86,94 @@ _SIGNATURES = {
     "ik_argmax": [_vp, _i, _vp, _i, _i, _vp, _vp],
     "ik_argmax_scratch_bytes": [],
     "ik_selftest_wait_expires": [_vp, _vp, _vp, _u64, _vp],
+    "ik_gemm_tcgen05_take_wait_record": [_vp],
     "ik_sample": [_vp, _i, _vp, _vp, _i, _i, _f, _i, _f, _f, _vp, _i, _u64, _vp, _vp, _vp],
 }
 
 _lib = None
 _status = {}
+
+
+# ---------------------------------------------------------------------------------------------
+# Per-kernel timing.  The reference times each operation of a forward pass when ITHACA_PROF is set
+# (src/model.cpp:1261-1307, src/cuda_tier.cpp:514-527).  Here, while a ``Profile`` is active, every call
+# into the kernel library is bracketed by CUDA events; the wrappers below say beforehand how many bytes the call has
+# to move and how many floating-point operations it has to do, so that a table can hold each call against the
+# device's peaks.  The events keep kernels from overlapping (no early launch), and nothing may be captured into
+# a graph meanwhile: it is a tool for looking at a step, not the way a step runs.
+class Profile:
+    def __init__(self):
+        self.records = []            # (label, start event, end event, bytes, flops)
+
+    def __enter__(self):
+        global _profile
+        if _profile is not None:
+            raise KernelError("a kernel profile is already being taken")
+        _profile = self
+        return self
+
+    def __exit__(self, *exc):
+        global _profile, _pending
+        _profile, _pending = None, None
+        return False
+
+    def rows(self):
+        """Per label, in order of first appearance: calls, microseconds, bytes, flops."""
+        torch.cuda.synchronize()
+        out = {}
+        for label, e0, e1, nbytes, flops in self.records:
+            r = out.setdefault(label, {"kernel": label, "calls": 0, "us": 0.0, "bytes": 0, "flops": 0})
+            r["calls"] += 1
+            r["us"] += e0.elapsed_time(e1) * 1e3
+            r["bytes"] += nbytes
+            r["flops"] += flops
+        return list(out.values())
+
+
+_profile: Optional[Profile] = None
+_pending = None                      # (label, bytes, flops) of the library call that comes next
+
+
+def profiling() -> bool:
+    return _profile is not None
+
+
+def _work(label: str, nbytes: int = 0, flops: int = 0) -> None:
+    global _pending
+    if _profile is not None:
+        _pending = (label, int(nbytes), int(flops))
+
+
+def _nbytes(*tensors) -> int:
+    return sum(t.numel() * t.element_size() for t in tensors if t is not None)
+
+
+class _TimedLibrary:
+    """Stands in for a loaded library while a profile is taken."""
+
+    def __init__(self, library):
+        self._library = library
+
+    def __getattr__(self, name):
+        fn = getattr(self._library, name)
+        if _profile is None or not name.startswith("ik_") or fn.argtypes is None or not fn.argtypes or fn.argtypes[-1] is not _vp:
+            return fn                                        # not a launch (no stream argument)
+
+        def call(*args):
+            global _pending
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            st = fn(*args)
+            e1.record()
+            label, nbytes, flops = _pending or (name[3:], 0, 0)
+            _pending = None
+            _profile.records.append((label, e0, e1, nbytes, flops))
+            return st
+        return call
+
+
+def timed(library):
+    return _TimedLibrary(library) if _profile is not None else library
 
 
 def device_status(device) -> torch.Tensor:
@@ -113,7 +197,7 @@ def lib():
             fn.argtypes = sig
             fn.restype = _i
         _lib = l
-    return _lib
+    return timed(_lib)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -124,6 +208,7 @@ def embed(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0, status: Op
     T, (V, d) = ids.numel(), table.shape
     if out is None:
         out = torch.empty((T, d), dtype=torch.float32, device=ids.device)
+    _work(f"embed {T}x{d}", T * d * (table.element_size() + 4))
     _check(lib().ik_embed(_ptr(ids), _ptr(table), _code(table), _ptr(out), T, d, V, scale, _ptr(status), _stream()),
            "embed")
     return out
@@ -141,6 +226,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
         _need(rows_in, "rows_in", torch.int32)
     if out is None:
         out = torch.empty((rows, d), dtype=out_dtype, device=x.device)
+    _work(f"rmsnorm {rows}x{d}", rows * d * (4 + out.element_size()) + d * 4)
     _check(lib().ik_rmsnorm(_ptr(x), _ptr(rows_in), _ptr(weight), _ptr(out), _code(out), rows, d, eps, _stream()),
            "rmsnorm")
     return out
@@ -155,6 +241,7 @@ def swiglu(gate_up: torch.Tensor, out_dtype: torch.dtype, out: Optional[torch.Te
         raise KernelError("swiglu: the input needs an even number of columns (gate then up)")
     if out is None:
         out = torch.empty((T, ff2 // 2), dtype=out_dtype, device=gate_up.device)
+    _work(f"swiglu {T}x{ff2 // 2}", _nbytes(gate_up, out))
     _check(lib().ik_swiglu(_ptr(gate_up), _ptr(out), _code(out), T, ff2 // 2, 1 if interleaved else 0, _stream()), "swiglu")
     return out
 
@@ -166,6 +253,18 @@ def fill_random(out: torch.Tensor, key: int, scale: float, offset: float) -> tor
     _check(lib().ik_fill_random(_ptr(out), _code(out), out.numel(), key & 0xFFFFFFFFFFFFFFFF, scale, offset, _stream()),
            "fill_random")
     return out
+
+
+def copy(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
+    """dst = src with this library's streaming copy kernel (sizes a multiple of 16 bytes)."""
+    _need(src, "src")
+    _need(dst, "dst")
+    n = src.numel() * src.element_size()
+    if n != dst.numel() * dst.element_size():
+        raise KernelError("copy: source and destination differ in size")
+    _work(f"copy {n >> 20} MiB", 2 * n)
+    _check(lib().ik_copy(_ptr(src), _ptr(dst), n, _stream()), "copy")
+    return dst
 
 
 def rope_append(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
@@ -184,6 +283,7 @@ def rope_append(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor, v
     n_pages, nkv, page_size, hd = k_pages.shape
     if nkv != n_kv_heads or hd != head_dim or v_pages.shape != k_pages.shape or v_pages.dtype != k_pages.dtype:
         raise KernelError("rope_append: the pages do not match the head sizes")
+    _work(f"rope_append {T}", _nbytes(qkv, q_out) + 2 * T * n_kv_heads * head_dim * k_pages.element_size())
     _check(lib().ik_rope_append(_ptr(qkv), _ptr(q_out), _code(q_out), _ptr(k_pages), _ptr(v_pages), _code(k_pages),
                                 _ptr(token_seq), _ptr(token_pos), _ptr(table), table.stride(0), _ptr(inv_freq), T,
                                 n_heads, n_kv_heads, head_dim, rotary_dim, pairing, page_size, n_pages,
@@ -206,6 +306,7 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     _need(out, "out", contiguous=False)
     if out.shape != (M, N) or out.stride(1) != 1:
         raise KernelError("gemm: the output has the wrong shape")
+    _work(f"gemm_simt {M}x{N}x{K}", M * K * x.element_size() + N * K * w.element_size() + M * N * out.element_size(), 2 * M * N * K)
     _check(lib().ik_gemm_simt(_ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), M, N, K, x.stride(0),
                               w.stride(0), out.stride(0), 1 if accumulate else 0, _stream()), "gemm_simt")
     return out
@@ -233,6 +334,7 @@ def gemm_bf16_mma(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] 
     _need(out, "out", contiguous=False)
     if out.shape != (M, n_out) or out.stride(1) != 1:
         raise KernelError("gemm: the output has the wrong shape")
+    _work(f"gemm_skinny{' +swiglu' if swiglu else ''} {M}x{N}x{K}", 2 * (M * K + N * K) + M * n_out * out.element_size(), 2 * M * N * K)
     st = lib().ik_gemm_bf16_mma(_ptr(x), _ptr(w), _ptr(out), _code(out), M, N, K, x.stride(0), w.stride(0),
                                 out.stride(0), 1 if accumulate else 0, kind, 1 if swiglu else 0, _stream())
     if st == -2:
@@ -314,6 +416,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
         splits = tcgen05_splits(M, N, K)
     partial = (stream_k_scratch(x.device) if splits == 0 else
                torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None)
+    _work(f"gemm_tcgen05{' +swiglu' if swiglu else ''} {M}x{N}x{K}", 2 * (M * K + N * K) + M * n_out * out.element_size(), 2 * M * N * K)
     st = lib().ik_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(out), _code(out), _ptr(partial), M, N, K, x.stride(0),
                                w.stride(0), out.stride(0), 1 if accumulate else 0, 1 if swiglu else 0, splits, _ptr(status),
                                _stream())
@@ -336,6 +439,7 @@ def rope_table(token_pos: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
     _need(inv_freq, "inv_freq", torch.float32)
     T, half = token_pos.numel(), inv_freq.numel()
     out = torch.empty((T, half, 2), dtype=torch.float32, device=token_pos.device)
+    _work(f"rope_table {T}", T * half * 8)
     _check(lib().ik_rope_table(_ptr(token_pos), _ptr(inv_freq), _ptr(out), T, half, _stream()), "rope_table")
     return out
 
@@ -365,6 +469,7 @@ def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages
     rs = RopeStore(_ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(cos_sin), _ptr(token_seq), _ptr(token_pos),
                    _ptr(table), _ptr(status), table.stride(0), n_heads, n_kv_heads, head_dim, page_size, n_pages,
                    1 if write_cache else 0)
+    _work(f"gemm_{'skinny' if M <= skinny_max else 'tcgen05'} +rope+cache {M}x{N}x{K}", 2 * (M * K + N * K + M * N), 2 * M * N * K)
     if M <= skinny_max:
         st = lib().ik_gemm_qkv_rope_mma(_ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), ctypes.byref(rs), _stream())
         kernels = 1
@@ -394,11 +499,27 @@ def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
         raise KernelError("attention: q has the wrong width")
     if out is None:
         out = torch.empty_like(q)
+    _work(f"attention_simt {T}x{n_heads}", _nbytes(q, out))
     _check(lib().ik_attention_simt(_ptr(q), _code(q), _ptr(k_pages), _ptr(v_pages), _code(k_pages), _ptr(out),
                                    _code(out), _ptr(token_seq), _ptr(token_pos), _ptr(table), table.stride(0), T,
                                    n_heads, nkv, hd, scale, window, page_size, n_pages, _ptr(status), _stream()),
            "attention_simt")
     return out
+
+
+def wait_records() -> str:
+    """Where the first wait of each tensor-core module gave up since the last call (read and cleared): text for an
+    error message, empty if none did."""
+    found = []
+    rec = (ctypes.c_int * 4)()
+    takers = [("matrix product", lib().ik_gemm_tcgen05_take_wait_record)]
+    from . import attention_bf16
+    for hd, m in attention_bf16._modules.items():
+        takers.append((f"attention (head size {hd})", m.ik_attn_take_wait_record))
+    for name, take in takers:
+        if take(rec) == 0 and rec[0] != 0:
+            found.append(f"{name}: wait site {rec[0]}, block {rec[1]}, count {rec[2]}, parity {rec[3]}")
+    return "; ".join(found)
 
 
 def selftest_wait_expires(status: torch.Tensor, limit_ns: int = 1_000_000) -> torch.Tensor:
@@ -437,6 +558,7 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, scratch: Op
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     if scratch is None:
         scratch = argmax_scratch(logits.device)
+    _work(f"argmax {rows}x{V}", rows * V * 4)
     _check(lib().ik_argmax(_ptr(logits), logits.stride(0), _ptr(out), rows, V, _ptr(scratch), _stream()), "argmax")
     return out
 
@@ -456,6 +578,7 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, r
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     if work is None:
         work = torch.empty((rows, V), dtype=torch.float32, device=logits.device)
+    _work(f"sample {rows}x{V}", 3 * rows * V * 4)
     _check(lib().ik_sample(_ptr(logits), logits.stride(0), _ptr(work), _ptr(out), rows, V, temperature, top_k, top_p,
                            repetition_penalty, _ptr(recent), n_recent, seed & 0xFFFFFFFFFFFFFFFF, _ptr(streams),
                            _ptr(counters), _stream()), "sample")

@@ -34,16 +34,37 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 // Waits for the phase with the given parity to complete.  Gives up after `limit_ns` (about a second unless the
 // caller says otherwise), or as soon as another thread of the block has given up, and returns false; the thread
 // that gives up first raises the block's abort flag and records the event in the status word.
+// The limit is counted in cycles of this SM's own clock (two per nanosecond asked for: at the clocks this part
+// runs at, between 1x and 2x the time asked for).  %globaltimer is not used for it: that counter is kept in step
+// with the host's clock from outside and may move by more than it ran.
 constexpr unsigned long long IK_WAIT_LIMIT_NS = 1000000000ull;
+__device__ __forceinline__ long long wait_clock() { return clock64(); }
+__device__ __forceinline__ bool wait_ran_out(long long c0, unsigned long long limit_ns) {
+    return (unsigned long long)(clock64() - c0) > 2ull * limit_ns;
+}
+
+// Where the first wait of this module gave up: [0] the wait's site number (0 = none yet), [1] the block's linear
+// index, [2] a number the site chose (a loop count), [3] the parity it waited for.  The host reads and clears it
+// when the status word says that a wait ran out.
+__device__ int ik_wait_record[4];
+__device__ __forceinline__ void note_wait_gave_up(int site, int info, int parity) {
+    if (atomicCAS(&ik_wait_record[0], 0, site) == 0) {
+        ik_wait_record[1] = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+        ik_wait_record[2] = info;
+        ik_wait_record[3] = parity;
+    }
+}
+
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          unsigned long long limit_ns = IK_WAIT_LIMIT_NS) {
+                                          unsigned long long limit_ns = IK_WAIT_LIMIT_NS, int site = 99, int info = 0) {
     if (mbar_test(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer();
+    const long long c0 = wait_clock();
     for (int spin = 0;; spin++) {
         if (mbar_test(bar, parity)) return true;
         if ((spin & 63) == 63) {
             if (*abort_flag) return false;
-            if (globaltimer() - t0 > limit_ns) {
+            if (wait_ran_out(c0, limit_ns)) {
+                note_wait_gave_up(site, info, (int)parity);
                 *abort_flag = 1;
                 ik_set_status(status, IK_STATUS_GEMM_TIMEOUT);
                 return false;
@@ -185,6 +206,15 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 typedef CUresult (*IkEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Copies the record of the first wait that gave up to the host and clears it on the device.
+inline int ik_take_wait_record(int* out4) {
+    int zero[4] = {0, 0, 0, 0};
+    cudaError_t e = cudaMemcpyFromSymbol(out4, ik_wait_record, sizeof(zero));
+    if (e != cudaSuccess) return (int)e;
+    e = cudaMemcpyToSymbol(ik_wait_record, zero, sizeof(zero));
+    return e == cudaSuccess ? IK_OK : (int)e;
+}
 
 inline IkEncodeTiled ik_encode_fn() {
     static IkEncodeTiled fn = nullptr;

@@ -167,9 +167,15 @@ class Engine:
         word = int(self._status_host[0])
         if word:
             self.runtime.status.zero_()
-            from .step import describe_status
+            from .step import describe_status, wait_detail
             from ..cache.pages import CacheError
-            raise CacheError("a kernel reported " + describe_status(word) + "; the results since the last check are not to be used")
+            raise CacheError("a kernel reported " + describe_status(word) + wait_detail(word)
+                             + "; the results since the last check are not to be used")
+
+    def profile_step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], want="last"):
+        """One step with CUDA events around every kernel call: returns (logits, rows); see ``engine.profile``."""
+        from .profile import profile_step
+        return profile_step(self, slots, tokens, want)
 
     def check_status(self) -> None:
         """Waits for the device and raises if a kernel has recorded something it refused to do."""

@@ -3,7 +3,9 @@
 Options the reference has keep its names and meanings: ``--model/-m``, ``--prompt/-p``,
 ``-n`` (default 128), ``--temp`` (default 0), ``--ctx/-c``, ``--bench`` (prompt of 512 and
 128 generated tokens, three runs after a warm-up of 64, printed as one ``BENCH`` line,
-src/main.cpp:1047-1068).  There is no tokenizer in this library, so a prompt is a list of
+src/main.cpp:1047-1068).  ``--profile`` stands for the reference's ``ITHACA_PROF`` timers
+(src/model.cpp:1261-1307): it runs the prompts as one step and then one more token each, with
+CUDA events around every kernel call, and prints both steps kernel by kernel.  There is no tokenizer in this library, so a prompt is a list of
 token ids (``-p "1,2,3"``); ``-p`` may be given several times for a batch.  After the run
 it prints ``[prompt N tok @ X tok/s | gen M tok @ Y tok/s]`` (src/main.cpp:1140).
 """
@@ -40,6 +42,10 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--max-tokens", type=int, default=None, help="cache size in positions (default: 8 sequences of ctx)")
     ap.add_argument("--bench", action="store_true", help="pp512 / tg128, three runs, one BENCH line")
+    ap.add_argument("--profile", action="store_true",
+                    help="time every kernel call of a prompt step and of a decode step and print the tables")
+    ap.add_argument("--peaks", metavar="FILE.json", default=None,
+                    help="with --profile: hbm_gbs and bf16_tflops to hold the kernels against (default: measured now)")
     ap.add_argument("--describe", action="store_true", help="print the model's layers and schedule, then exit")
     return ap
 
@@ -71,6 +77,30 @@ def _bench(eng, name: str, load_s: float) -> None:
     print(f"BENCH model={name} load_s={load_s:.2f} pp512={sum(pp) / 3:.1f} tg128={sum(tg) / 3:.2f} vram_mb={vram:.0f}")
 
 
+def _profile(eng, prompts: List[List[int]], peaks_file: Optional[str]) -> None:
+    from .profile import format_table, measure_peaks
+    if peaks_file:
+        with open(peaks_file) as f:
+            peaks = json.load(f)
+    else:
+        peaks = measure_peaks(eng.runtime.device)
+    print(f"peaks: {peaks['hbm_gbs']} GB/s, {peaks['bf16_tflops']} TFLOP/s bfloat16"
+          + (f" ({peaks['how']})" if "how" in peaks else ""))
+    slots = [eng.alloc_slot() for _ in prompts]
+    eng.step(slots, prompts, "last")                       # warm-up: whatever still has to be compiled or loaded
+    for s in slots:
+        eng.truncate(s, 0)
+    logits, rows = eng.profile_step(slots, prompts, "last")
+    print(format_table(rows, peaks, f"prompt step: {sum(len(p) for p in prompts)} tokens of {len(prompts)} sequences"))
+    nxt = [[int(t)] for t in logits.argmax(-1).tolist()]
+    eng.profile_step(slots, nxt, "last")
+    _, rows = eng.profile_step(slots, nxt, "last")
+    print(format_table(rows, peaks, f"decode step: one token of {len(prompts)} sequences"))
+    eng.check_status()
+    for s in slots:
+        eng.free_slot(s)
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     args = build_parser().parse_args(argv)
     t0 = time.perf_counter()
@@ -92,6 +122,9 @@ def main(argv: Optional[List[str]] = None) -> int:
             prompts += [_ids(line) for line in f if line.strip()]
     if not prompts:
         raise SystemExit("give at least one --prompt (token ids)")
+    if args.profile:
+        _profile(eng, prompts, args.peaks)
+        return 0
     stops = _ids(args.stop_ids) if args.stop_ids is not None else None
     out = eng.generate(prompts, max_tokens=args.n, temp=args.temp, top_k=args.top_k, top_p=args.top_p,
                        rep_pen=args.rep_pen, seed=args.seed, stop_token_ids=stops)

@@ -162,12 +162,21 @@ class Stepper:
             v = int(st.item())
             if v != 0:
                 st.zero_()
-                raise CacheError("a kernel reported " + describe_status(v))
+                raise CacheError("a kernel reported " + describe_status(v) + wait_detail(v))
 
 
 STATUS_EVENTS = {1: "a token id outside the vocabulary", 2: "a cache write without a page",
                  3: "a cache read without a page", 4: "a matrix-product block that gave up waiting for its data",
                  5: "shared memory that is not aligned for the tensor-core tiles"}
+
+
+def wait_detail(word: int) -> str:
+    """For a wait that ran out: which wait of which kernel it was."""
+    if not word & (1 << 3):
+        return ""
+    from ..csrc import ops
+    where = ops.wait_records()
+    return f" [{where}]" if where else ""
 
 
 def describe_status(word: int) -> str:

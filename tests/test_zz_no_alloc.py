@@ -10,6 +10,7 @@ scratch supplied by the caller) returns, on two calls in a row that share the ar
 The file is named so that pytest collects it last.
 """
 import ctypes
+import gc
 
 import pytest
 import torch
@@ -69,13 +70,17 @@ def test_the_static_entry_point_takes_no_device_memory():
     assert st == 0
     torch.cuda.synchronize()
     out = torch.empty(8, dtype=torch.int32, device=DEV)
-    free0, held0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+    gc.collect()                     # tensors of earlier tests that are still waiting to be collected go now, not in between
+    torch.cuda.synchronize()
+    count = lambda: torch.cuda.memory_stats()["allocation.all.allocated"]          # allocations torch has ever made
+    free0, made0 = torch.cuda.mem_get_info()[0], count()
     for _ in range(3):
         st = fn(logits.data_ptr(), logits.stride(0), out.data_ptr(), 8, 5003, 0.8, 40, 0.9, 1.1, recent.data_ptr(), 64, 99,
                 streams.data_ptr(), counters.data_ptr(), torch.cuda.current_stream().cuda_stream)
         assert st == 0
     torch.cuda.synchronize()
-    assert torch.cuda.mem_get_info()[0] == free0 and torch.cuda.memory_allocated() == held0
+    assert torch.cuda.mem_get_info()[0] >= free0, "the driver's free device memory went down during the calls"
+    assert count() == made0, "torch's allocator was asked for memory during the calls"
 
 
 def test_a_request_beyond_the_static_array_is_refused(capfd):
