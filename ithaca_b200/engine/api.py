@@ -186,9 +186,14 @@ class Engine:
     def free_slots(self) -> int:
         return self.cache.max_slots - self.cache.table.n_slots_in_use()
 
-    def room_for(self, lengths: Sequence[int]) -> bool:
+    def room_for(self, lengths: Sequence[int], slots: Optional[Sequence[Optional[int]]] = None) -> bool:
         page = self.cache.page_size
-        need = sum(-(-n // page) for n in lengths)
+        need = 0
+        for i, n in enumerate(lengths):
+            have = 0
+            if slots is not None and slots[i] is not None:
+                have = -(-int(self.cache.table._reserved[slots[i]]) // page)      # pages the slot holds already
+            need += max(0, -(-n // page) - have)
         return all(need <= pool.n_free for pool in self.cache.table.pools) if self.cache.table.pools else True
 
     def step_and_sample(self, slots, tokens, streams, counters, recent) -> List[int]:
@@ -202,10 +207,10 @@ class Engine:
 
     # -- generation ----------------------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], options: Optional[GenerationOptions] = None,
-                 on_token: Optional[Callable[[int, int], bool]] = None, **kw) -> List[List[int]]:
+                 on_token: Optional[Callable[[int, int], bool]] = None, resume=None, **kw) -> List[List[int]]:
         """Generates for every prompt (lists of token ids); returns the new ids per prompt.
         Keyword arguments are ``GenerationOptions`` fields.  Counters of the run are in
-        ``last_stats``."""
+        ``last_stats``.  ``resume``: see ``generate_loop`` (``Session`` uses it)."""
         if options is None:
             options = GenerationOptions(**kw)
         elif kw:
@@ -213,8 +218,13 @@ class Engine:
         self._sampler = Sampler(options.sampling(), self.runtime.device)
         try:
             out, stats = generate_loop(prompts, options, self, stop_token_ids=self.model.spec.stop_token_ids,
-                                       on_token=on_token)
+                                       on_token=on_token, resume=resume)
         finally:
             self._settle()
         self.last_stats = stats
         return out
+
+    def session(self) -> "Session":
+        """A sequence that lives on between calls to ``generate`` and keeps its cache: see ``Session``."""
+        from .session import Session
+        return Session(self)

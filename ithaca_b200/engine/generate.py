@@ -49,6 +49,7 @@ class GenStats:
     decode_seconds: float = 0.0
     batches: int = 0
     steps: int = 0
+    reused_tokens: int = 0          # prompt positions found in the cache (src/chat.h:27 ``reused``)
 
     @property
     def prefill_tps(self) -> float:
@@ -62,8 +63,9 @@ class GenStats:
 class Backend(Protocol):
     context_length: int          # the most positions one sequence may hold
 
-    def room_for(self, lengths: Sequence[int]) -> bool:
-        """Can sequences that will grow to these lengths live at the same time?"""
+    def room_for(self, lengths: Sequence[int], slots: Optional[Sequence[Optional[int]]] = None) -> bool:
+        """Can sequences that will grow to these lengths live at the same time?  ``slots[i]`` names the slot
+        sequence i already lives in (what that slot holds needs no new room), or None."""
 
     def free_slots(self) -> int: ...
     def alloc_slot(self) -> int: ...
@@ -79,6 +81,8 @@ class _Running:
     request: int
     slot: int
     budget: int
+    cached: int = 0            # positions of the prompt that the slot held already (a resumed request)
+    owned: bool = True         # the loop took the slot and gives it back; a resumed request's slot is its caller's
     out: List[int] = field(default_factory=list)
     recent: List[int] = field(default_factory=list)
     next_token: int = -1
@@ -92,26 +96,40 @@ def budget_for(prompt_len: int, max_tokens: int, context_length: int) -> int:
 
 
 def next_batch(pending: Sequence[int], prompts: Sequence[Sequence[int]], budgets: Sequence[int], backend: Backend,
-               max_batch: Optional[int]) -> List[int]:
+               max_batch: Optional[int], resume: Optional[Sequence[Optional[tuple]]] = None) -> List[int]:
     """The longest run of pending requests, in order, that fits the free slots and the
-    cache when every one of them grows to its full budget."""
+    cache when every one of them grows to its full budget.  A resumed request brings its slot."""
     chosen: List[int] = []
-    limit = backend.free_slots() if max_batch is None else min(max_batch, backend.free_slots())
+    fresh = 0
     for r in pending:
-        if len(chosen) >= limit:
+        held = resume[r][0] if resume is not None and resume[r] is not None else None
+        if max_batch is not None and len(chosen) >= max_batch:
+            break
+        if held is None and fresh >= backend.free_slots():
             break
         grown = [len(prompts[c]) + budgets[c] for c in chosen + [r]]
-        if not backend.room_for(grown):
+        if resume is None:
+            fits = backend.room_for(grown)
+        else:
+            fits = backend.room_for(grown, [resume[c][0] if resume[c] is not None else None for c in chosen + [r]])
+        if not fits:
             break
         chosen.append(r)
+        fresh += held is None
     return chosen
 
 
 def generate_loop(prompts: Sequence[Sequence[int]], options: GenerationOptions, backend: Backend,
                   stop_token_ids: Sequence[int] = (), on_token: Optional[Callable[[int, int], bool]] = None,
-                  clock: Callable[[], float] = time.perf_counter):
+                  clock: Callable[[], float] = time.perf_counter,
+                  resume: Optional[Sequence[Optional[tuple]]] = None):
     """Returns (generated ids per request, GenStats).  ``on_token(request, id)`` may
-    return False to end that request (the reference's ``on_text`` callback, src/chat.cpp:481)."""
+    return False to end that request (the reference's ``on_text`` callback, src/chat.cpp:481).
+
+    ``resume[r] = (slot, n)``: request r goes on in a slot its caller holds, whose first n positions
+    are the first n tokens of its prompt already (the reference's reuse of the cache for a shared
+    prefix, src/chat.cpp:311-318): only the rest of the prompt is evaluated, and the slot stays
+    with the caller when the request ends.  n must be less than the prompt's length."""
     stops = set(options.stop_token_ids if options.stop_token_ids is not None else stop_token_ids)
     ctx = backend.context_length
     for n, p in enumerate(prompts):
@@ -119,6 +137,8 @@ def generate_loop(prompts: Sequence[Sequence[int]], options: GenerationOptions, 
             raise ValueError(f"request {n}: empty prompt")                    # src/chat.cpp:298
         if len(p) > ctx:
             raise ValueError(f"request {n}: the prompt of {len(p)} tokens is longer than the context of {ctx}")
+        if resume is not None and resume[n] is not None and not 0 <= resume[n][1] < len(p):
+            raise ValueError(f"request {n}: {resume[n][1]} cached positions do not leave a token of the prompt to evaluate")
     budgets = [budget_for(len(p), options.max_tokens, ctx) for p in prompts]
     results: List[List[int]] = [[] for _ in prompts]
     stats = GenStats()
@@ -143,25 +163,32 @@ def generate_loop(prompts: Sequence[Sequence[int]], options: GenerationOptions, 
         return True
 
     while pending:
-        batch = next_batch(pending, prompts, budgets, backend, options.max_batch)
+        batch = next_batch(pending, prompts, budgets, backend, options.max_batch, resume)
         if not batch:
             raise RuntimeError(f"request {pending[0]} does not fit the cache even alone "
                                f"({len(prompts[pending[0]])} prompt tokens + {budgets[pending[0]]} new)")
         pending = pending[len(batch):]
         stats.batches += 1
-        running = [_Running(r, backend.alloc_slot(), budgets[r]) for r in batch]
+        running = []
+        for r in batch:
+            if resume is not None and resume[r] is not None:
+                running.append(_Running(r, resume[r][0], budgets[r], cached=resume[r][1], owned=False))
+            else:
+                running.append(_Running(r, backend.alloc_slot(), budgets[r]))
         try:
             # requests with no budget produce nothing and need no step
-            for run in [x for x in running if x.budget == 0]:
+            for run in [x for x in running if x.budget == 0 and x.owned]:
                 backend.free_slot(run.slot)
             running = [x for x in running if x.budget > 0]
             if running:
                 t0 = clock()
-                toks = backend.step_and_sample([x.slot for x in running], [list(prompts[x.request]) for x in running],
+                toks = backend.step_and_sample([x.slot for x in running],
+                                               [list(prompts[x.request][x.cached:]) for x in running],
                                                [x.request for x in running], [0] * len(running),
                                                [x.recent for x in running])
                 stats.prefill_seconds += clock() - t0
-                stats.prompt_tokens += sum(len(prompts[x.request]) for x in running)
+                stats.prompt_tokens += sum(len(prompts[x.request]) - x.cached for x in running)
+                stats.reused_tokens += sum(x.cached for x in running)
                 stats.steps += 1
                 t1 = clock()
                 while True:
@@ -171,7 +198,8 @@ def generate_loop(prompts: Sequence[Sequence[int]], options: GenerationOptions, 
                             still.append(run)
                         else:
                             results[run.request] = run.out
-                            backend.free_slot(run.slot)
+                            if run.owned:
+                                backend.free_slot(run.slot)
                             run.slot = -1
                     running = still
                     if not running:
@@ -183,6 +211,6 @@ def generate_loop(prompts: Sequence[Sequence[int]], options: GenerationOptions, 
                 stats.decode_seconds += clock() - t1
         finally:
             for run in running:
-                if run.slot >= 0:
+                if run.slot >= 0 and run.owned:
                     backend.free_slot(run.slot)
     return results, stats

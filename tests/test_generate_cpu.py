@@ -17,8 +17,9 @@ class FakeBackend:
     def free_slots(self):
         return len(self.free)
 
-    def room_for(self, lengths):
-        used = sum(-(-l // self.page) for l in self.lengths.values())
+    def room_for(self, lengths, slots=None):
+        mine = set(s for s in (slots or []) if s is not None)
+        used = sum(-(-l // self.page) for s, l in self.lengths.items() if s not in mine)
         return used + sum(-(-l // self.page) for l in lengths) <= self.n_pages
 
     def alloc_slot(self):
@@ -121,6 +122,24 @@ def test_slots_are_freed_when_a_step_fails():
     with pytest.raises(RuntimeError, match="boom"):
         generate_loop([[1], [2]], GenerationOptions(max_tokens=3), be)
     assert be.lengths == {} and len(be.free) == 3
+
+
+def test_a_resumed_request_feeds_only_what_its_slot_lacks_and_keeps_the_slot():
+    """Request 1 goes on in a slot that already holds 6 of its 9 prompt tokens: the prompt step brings the other
+    3, the request decodes like any other, and at the end its slot is still the caller's while the other is freed."""
+    be = FakeBackend({0: [5, 6, 7], 1: [8, 9, 10]})
+    held = be.alloc_slot()
+    be.lengths[held] = 6
+    out, st = generate_loop([[1] * 4, [2] * 9], GenerationOptions(max_tokens=3), be, resume=[None, (held, 6)])
+    assert out == [[5, 6, 7], [8, 9, 10]]
+    assert be.calls[0][0] == [4, 3] and st.prompt_tokens == 7 and st.reused_tokens == 6
+    assert list(be.lengths) == [held] and be.lengths[held] == 6 + 3 + 2     # the last sampled token is not evaluated
+    with pytest.raises(ValueError, match="cached positions"):
+        generate_loop([[2] * 9], GenerationOptions(max_tokens=3), be, resume=[(held, 9)])
+    # a held slot needs no free slot: with none free the resumed request still runs, a fresh one has to wait its turn
+    be2 = FakeBackend({0: [1, 1], 1: [2, 2]}, n_slots=1)
+    h = be2.alloc_slot()
+    assert next_batch([0, 1], [[1] * 3, [1] * 3], [2, 2], be2, None, [(h, 0), None]) == [0]
 
 
 def test_decode_chunk_choice_is_sane():

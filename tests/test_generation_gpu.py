@@ -162,3 +162,49 @@ def test_command_line(models, tmp_path):
     want = [P.generate(pr, cfg, tensors, 5, repetition_penalty=1.1) for pr in ([1, 2, 3], [9, 8, 7, 6])]
     assert got == want
     assert "[prompt 7 tok @" in p.stderr and "gen 10 tok @" in p.stderr
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("C", "float32"), ("B", "bfloat16")])
+def test_a_session_reuses_the_prefix_its_next_prompt_shares(models, name, dtype):
+    """Three turns in one slot, beside another request that the engine serves in between.  Turn 2's prompt is turn
+    1's prompt, its reply and new tokens: everything up to the reply's last evaluated token is found in the cache.
+    Turn 3 changes a token in the middle: the cache is cut back to there.  In float32 every turn's ids equal the
+    plain implementation's for the whole prompt; Tiny C (a window) falls back to starting over when the pages it
+    would need are gone, with the same ids."""
+    from ithaca_b200 import Engine
+    (d,) = models[name]
+    cfg, tensors = load_plain(d)
+    V = cfg["vocab_size"]
+    eng = Engine(d, dtype=dtype, max_tokens=64 * 12)
+    opts = dict(max_tokens=8, temp=0.0, rep_pen=1.0, stop_token_ids=[])
+    with eng.session() as chat:
+        p1 = random_ids(40, V, 501)
+        r1 = chat.generate(p1, **opts)
+        assert chat.reused_last == 0 and len(chat.tokens) == 40 + 7          # the eighth token was sampled, not evaluated
+        other = eng.generate([random_ids(9, V, 502)], **opts)                # the engine serves someone else meanwhile
+        p2 = p1 + r1 + random_ids(30, V, 503)
+        r2 = chat.generate(p2, **opts)
+        reused2 = chat.reused_last
+        p3 = list(p2)
+        p3[55] = (p3[55] + 1) % V
+        p3 = p3 + r2[:3]
+        r3 = chat.generate(p3, **opts)
+        reused3 = chat.reused_last
+        assert eng.last_stats.reused_tokens == reused3 and eng.last_stats.prompt_tokens == len(p3) - reused3
+        if cfg.get("use_sliding_window"):
+            assert reused2 in (0, 47) and reused3 in (0, 55)
+        else:
+            assert reused2 == 47 and reused3 == 55
+        if dtype == "float32":
+            for p, r in ((p1, r1), (p2, r2), (p3, r3)):
+                assert r == P.generate(p, cfg, tensors, 8, repetition_penalty=1.0)
+            assert other[0] == P.generate(random_ids(9, V, 502), cfg, tensors, 8, repetition_penalty=1.0)
+        else:
+            # bfloat16: the logits behind the reused prefix stay within the 16-bit tolerance of the plain ones
+            s = chat.slot
+            eng.truncate(s, len(p3) - 1)
+            lg = eng.step([s], [[p3[-1]]], "last").cpu().numpy()
+            assert rel_err(lg, plain_logits(cfg, tensors, p3)[-1:]) <= REL[dtype]
+    eng.check_status()
+    assert eng.cache.table.n_slots_in_use() == 0
+    eng.cache.table.check_consistent()
