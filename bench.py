@@ -320,6 +320,65 @@ def products_run(cfg, tokens, reps):
     return out
 
 
+def products_sweep(cfg, token_counts, reps):
+    """A layer's four products at decode-sized token counts: what the dispatcher picks, the warp-level kernel, the
+    tcgen05 kernel under each way of sharing out its work (whole tiles, 2 to 8 K slices, stream-K), and cuBLAS.  Each
+    variant is captured into a CUDA graph of one call per weight copy (copies larger than L2 together) and the
+    graph is replayed, so the figures are device times of back-to-back launches, not of the host's call rate."""
+    import torch
+    from ithaca_b200.csrc import gemm_bf16, ops
+    dev = "cuda:0"
+    d, ff = cfg["hidden_size"], cfg["intermediate_size"]
+    qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
+    status = ops.device_status(dev)
+    ops.stream_k_scratch(dev)
+    out = []
+    for name, n, k in [("qkv", qkv, d), ("o", d, cfg["num_attention_heads"] * cfg["head_dim"]), ("gate_up", 2 * ff, d), ("down", d, ff)]:
+        copies = max(2, min(8, int(300e6 // (n * k * 2)) + 1))
+        ws = [torch.randn((n, k), device=dev).to(torch.bfloat16) for _ in range(copies)]
+        for tokens in token_counts:
+            x = torch.randn((tokens, k), device=dev).to(torch.bfloat16)
+            y = torch.empty((tokens, n), device=dev, dtype=torch.float32)
+            yb = torch.empty((tokens, n), device=dev, dtype=torch.bfloat16)
+            variants = {"auto": lambda w: gemm_bf16.gemm(x, w, out=y)}
+            if tokens <= 64:
+                variants["skinny"] = lambda w: ops.gemm_bf16_mma(x, w, out=y, kind=1)
+            for s, label in ((1, "tc_tiles"), (2, "tc_k2"), (4, "tc_k4"), (8, "tc_k8"), (0, "tc_stream_k"),
+                             (-2, "tc_cl2"), (-3, "tc_cl3"), (-4, "tc_cl4")):
+                if s < 0 and not ops.tcgen05_cluster_fits(tokens, n, k, -s):
+                    continue
+                variants[label] = (lambda s_: lambda w: ops.gemm_tcgen05(x, w, out=y, status=status, splits=s_))(s)
+            variants["cublas"] = lambda w: torch.matmul(x, w.T, out=yb)
+            row = {"product": name, "rows": n, "k": k, "tokens": tokens, "picked_splits": ops.tcgen05_splits(tokens, n, k),
+                   "picked_skinny": gemm_bf16.takes_skinny(tokens, n, k), "ideal_us": round(n * k * 2 / pk_hbm() / 1e3, 1)}
+            for label, fn in variants.items():
+                for w in ws[:2]:
+                    fn(w)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    for w in ws:
+                        fn(w)
+                g.replay()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(reps):
+                    g.replay()
+                b.record()
+                torch.cuda.synchronize()
+                row[label] = round(a.elapsed_time(b) / (reps * copies) * 1e3, 1)
+                del g
+            out.append(row)
+        del ws
+    out.append({"status": int(status.item())})
+    return out
+
+
+def pk_hbm():
+    return peaks()["hbm_gbs"]
+
+
 def attention_run(cfg, reps):
     """The prefill attention kernel alone, on one sequence in a shuffled paged cache: the whole prompt, a chunk
     behind cached tokens, and one query tile per block in front of a long context with two blocks for every SM."""
@@ -376,6 +435,8 @@ def main():
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES),
                     help="layer sizes: 8b is the benchmark's configuration, the others are for comparison")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points and the two other workloads")
+    ap.add_argument("--tokens", default=None,
+                    help="with --only products: token counts, e.g. 16,32,64: a sweep over the ways the products can run")
     ap.add_argument("--config", default=None, choices=["1b-unequal", "13b-long"],
                     help="run one of the other workloads alone and print its figures")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention", "products"],
@@ -402,6 +463,10 @@ def main():
         return 0
     shape_name, shape_cfg = SHAPES[args.shape]
     cfg = dict(shape_cfg)
+    if args.only == "products" and args.tokens:
+        counts = [int(t) for t in args.tokens.split(",")]
+        print(json.dumps({"only": "products", "model": shape_name, "sweep": products_sweep(cfg, counts, reps=max(3, min(args.steps, 20)))}))
+        return 0
     if args.only == "products":
         print(json.dumps({"only": "products", "model": shape_name, "tokens": PREFILL_TOKENS,
                           "cases": products_run(cfg, PREFILL_TOKENS, reps=max(1, min(args.steps, 5)))}))

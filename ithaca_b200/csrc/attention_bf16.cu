@@ -811,7 +811,7 @@ IK_EXPORT int ik_attn_decode(const void* q, const void* k_pages, const void* v_p
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     dim3 grid2(B, nh);
-    IK_RETURN_IF_ERROR(ik_launch(attn_combine_kernel, grid2, HD < 128 ? HD : 128, 0, stream, part_o, part_ml, (bf16*)out, kv_lens, nh, window,
+    IK_RETURN_IF_ERROR(ik_launch_family(IK_FAMILY_ATTENTION_MERGE, attn_combine_kernel, grid2, HD < 128 ? HD : 128, 0, stream, part_o, part_ml, (bf16*)out, kv_lens, nh, window,
                                                                     chunk_pages, n_splits));
     IK_LAUNCH_STATUS();
 }

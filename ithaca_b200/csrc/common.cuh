@@ -144,6 +144,7 @@ static inline int ik_sm_count() {
 #define IK_FAMILY_ATTENTION 4
 #define IK_FAMILY_TCGEN05 8
 #define IK_FAMILY_SAMPLING 16
+#define IK_FAMILY_ATTENTION_MERGE 32     // the kernel that merges the chunks of decode attention
 #ifndef IK_FAMILY
 #define IK_FAMILY IK_FAMILY_ELEMENTWISE
 #endif

@@ -28,6 +28,11 @@
 // at the very start of their run, so the wait is short, cannot be circular, and the result does not depend on
 // timing.  The wait is bounded like the mbarrier waits.  Flags are cleared by their reader.
 //
+// Few tiles (a small matrix and few tokens): a cluster of 2 to 4 blocks shares one tile, each block taking a slice
+// of K.  The blocks of ranks 1.. write their raw sums into the shared memory of the block of rank 0 (distributed
+// shared memory) and arrive on a barrier there; rank 0 adds them to its own in rank order and runs the epilogue.
+// No partial sums go through global memory and no second kernel runs.
+//
 // Every wait on an mbarrier is bounded: after about a second without progress the waiting
 // thread sets the status word to IK_STATUS_GEMM_TIMEOUT, raises the block's abort flag and
 // every role leaves its loop; TMEM is freed and the block returns.  Blocks that start after
@@ -50,6 +55,12 @@ template <int BN> struct Cfg {
     static constexpr int ACC_COLS = BN < 32 ? 32 : BN;           // TMEM columns of one accumulator
     static constexpr int TMEM_COLS = 2 * ACC_COLS;               // two accumulators: one is drained while the other fills
     static constexpr int SMEM = STAGES * STAGE + 1024 /* alignment slack */ + 256 /* barriers */;
+    // cluster mode: room for the other ranks' sums ([rank - 1][BN][128] floats) beside a shorter ring of stages
+    static constexpr int RED_SLOTS = BN <= 64 ? 3 : (BN <= 128 ? 1 : 0);
+    static constexpr int RED_BYTES = RED_SLOTS * BN * BM * 4;
+    static constexpr int CL_ROOM = 232448 - 1024 - 256 - 4 * BN * 4 /* static */ - RED_BYTES;
+    static constexpr int CL_STAGES = CL_ROOM / STAGE > 8 ? 8 : CL_ROOM / STAGE;
+    static constexpr int CL_SMEM = CL_STAGES * STAGE + RED_BYTES + 1024 + 256;
 };
 
 // Persistent: one block per SM of the device.  Stream-K scratch: a flag per block and epilogue warp (room for 1024
@@ -67,7 +78,7 @@ struct Work {
 
 // The sequence of Work of one block.  Every role of the block walks it on its own.
 struct Walk {
-    bool sk;
+    bool sk, cl = false, cl_done = false;   // cl: one piece of work per block: tile blockIdx.x / n_splits, K slice = rank in the cluster
     int tiles_m, tiles_n, nkb_total, kb_per_split;
     int item, n_items;                // data-parallel: items blockIdx.x, + gridDim.x, ...; item -> (K slice, weight tile, token tile)
     long long u, u_end, n_units;      // stream-K: this block's share [u, u_end) of all (tile, K step) units, token tile fastest
@@ -79,7 +90,15 @@ struct Walk {
     }
     __device__ long long share_begin(int block) const { return n_units * block / gridDim.x; }
     __device__ bool next(Work& w) {
-        if (sk) {
+        if (cl) {
+            if (cl_done) return false;
+            cl_done = true;
+            const int n_splits = n_items / (tiles_m * tiles_n);
+            w.tile = blockIdx.x / n_splits;
+            w.z = blockIdx.x % n_splits;
+            w.kb0 = w.z * kb_per_split;
+            w.nkb = min(kb_per_split, nkb_total - w.kb0);
+        } else if (sk) {
             if (u >= u_end) return false;
             w.tile = (int)(u / nkb_total);
             w.kb0 = (int)(u - (long long)w.tile * nkb_total);
@@ -131,6 +150,17 @@ __device__ __forceinline__ bool flag_wait(const int* flag, volatile int* abort_f
     }
 }
 
+// Built with -DIK_TIMELINE, the product stamps the nanosecond clock at the stations of a block's life (for the first
+// 1024 blocks of the launch): 0 entry, 1 barriers and TMEM set up, 2 the kernel before has finished, 3 the first
+// stage has landed, 4 the last product is issued, 5 the block's last accumulator is complete, 6 its epilogue is done,
+// 7 the block leaves.  ik_gemm_tcgen05_timeline copies the stamps out.  Not compiled otherwise.
+#ifdef IK_TIMELINE
+__device__ unsigned long long ik_timeline[1024][8];
+#define IK_STAMP(i) do { if (blockIdx.x < 1024) ik_timeline[blockIdx.x][i] = globaltimer(); } while (0)
+#else
+#define IK_STAMP(i) do { } while (0)
+#endif
+
 // map_w: [N rows, K] box {64, 128};  map_x: [M rows, K] box {64, BN}.
 // out: Y (float or bf16) when partial == nullptr, else partial sums [splits][M][N] float.
 //
@@ -139,30 +169,40 @@ __device__ __forceinline__ bool flag_wait(const int* flag, volatile int* abort_f
 // that order, so they run at the same time on different SMs and the weight tile is fetched from
 // HBM once.  The accumulator is double-buffered in TMEM: while the epilogue warps drain tile i,
 // the MMA warp already fills the other buffer with tile i + 1.
-template <int BN, typename TY>
+// CL: the cluster mode described at the top (n_splits blocks per tile, partial == nullptr, one piece of work per block).
+template <int BN, typename TY, bool CL>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     TY* __restrict__ Y, float* __restrict__ partial, int M, int N, int K, int ldy, int accumulate,
-                    int swiglu, int kb_per_split, int n_splits, int stream_k, int* status, const IkRopeStore rope) {
+                    int swiglu, int kb_per_split, int n_splits, int stream_k, int* status, const IkRopeStore rope, int bn) {
+    // bn <= BN: the width of a token tile in use (a multiple of 16): tiles lie bn tokens apart, bn rows of tokens are
+    // loaded per stage and the products are bn columns wide; BN is the room a stage and an accumulator have.
     typedef Cfg<BN> C;
     extern __shared__ unsigned char smem_raw[];
     __shared__ int rope_rows[4][BN];                   // per epilogue warp: the cache row of each of the tile's tokens
-    if (ik_status_has(status, IK_STATUS_GEMM_TIMEOUT)) return;     // an earlier block gave up
+    if (threadIdx.x == 0) IK_STAMP(0);
+    // (in cluster mode every block goes on to the cluster's barrier below; its waits are bounded all the same)
+    if (!CL && ik_status_has(status, IK_STATUS_GEMM_TIMEOUT)) return;     // an earlier block gave up
+    constexpr int NST = CL ? C::CL_STAGES : C::STAGES;
     unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = (uint64_t*)(tiles + C::STAGES * C::STAGE);
-    uint64_t* empty = full + C::STAGES;
-    uint64_t* acc_full = empty + C::STAGES;            // [2] accumulator written, ready to be drained
+    float* const red = (float*)(tiles + NST * C::STAGE);                  // cluster mode: [rank - 1][BN][128] sums of the other ranks
+    uint64_t* full = (uint64_t*)(tiles + NST * C::STAGE + (CL ? C::RED_BYTES : 0));
+    uint64_t* empty = full + NST;
+    uint64_t* acc_full = empty + NST;                  // [2] accumulator written, ready to be drained
     uint64_t* acc_empty = acc_full + 2;                // [2] accumulator drained, free to be overwritten
-    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    uint64_t* red_full = acc_empty + 2;                // cluster mode, rank 0: the other ranks' sums have arrived
+    uint32_t* tmem_slot = (uint32_t*)(red_full + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_n = (N + BM - 1) / BM, tiles_m = (M + BN - 1) / BN;
+    const int tiles_n = (N + BM - 1) / BM, tiles_m = (M + bn - 1) / bn;
+    const int stage_bytes = C::A_BYTES + bn * BK * 2;
     const int nkb_total = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::STAGES; s++) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+        for (int s = 0; s < NST; s++) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
         for (int b = 0; b < 2; b++) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 128); }
+        mbar_init(red_full, CL ? (n_splits - 1) * 128 : 1);         // one arrival per epilogue thread of every other rank
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" :: "l"(&map_w) : "memory");
@@ -177,20 +217,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    const Walk walk_init(stream_k != 0, tiles_m, tiles_n, nkb_total, kb_per_split, n_splits);
+    if (CL) cluster_sync();                            // every block's barriers exist before another block arrives on them
+    Walk walk_first(stream_k != 0, tiles_m, tiles_n, nkb_total, kb_per_split, n_splits);
+    walk_first.cl = CL;
+    const Walk walk_init = walk_first;
     // Weights are written by no kernel: the first stages' weight tiles are asked for before the wait for the kernel
     // before this one (whose results are the tokens), so a product launched early has them on the way by then.
     int pre_issued = 0;
     if (threadIdx.x == 0) {
         Walk walk = walk_init;
-        for (Work w; pre_issued < C::STAGES && walk.next(w);)
-            for (int i = 0; i < w.nkb && pre_issued < C::STAGES; i++, pre_issued++) {
-                mbar_expect_tx(full + pre_issued, C::STAGE);
+        for (Work w; pre_issued < NST && walk.next(w);)
+            for (int i = 0; i < w.nkb && pre_issued < NST; i++, pre_issued++) {
+                mbar_expect_tx(full + pre_issued, stage_bytes);
                 tma_load_2d(tiles + pre_issued * C::STAGE, &map_w, (w.kb0 + i) * BK, w.nt * BM, full + pre_issued);
             }
     }
+    if (threadIdx.x == 0) IK_STAMP(1);
     ik_pdl_wait();                                     // barriers, TMEM and the first weights are under way while the kernel before finishes
     ik_pdl_launch_dependents();
+    if (threadIdx.x == 0) IK_STAMP(2);
 
     float* const slice_sums = stream_k ? nullptr : partial;           // data-parallel K slices: [slice][M][N]
     int* const piece_flags = stream_k ? reinterpret_cast<int*>(partial) : nullptr;                        // [block][4]
@@ -202,13 +247,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             bool ok = true;
             Walk walk = walk_init;
             for (Work w; ok && walk.next(w);) {
-                const int n0 = w.nt * BM, m0 = w.mt * BN, kb0 = w.kb0, nkb = w.nkb;
+                const int n0 = w.nt * BM, m0 = w.mt * bn, kb0 = w.kb0, nkb = w.nkb;
                 for (int i = 0; i < nkb; i++, it++) {
-                    const int s = it % C::STAGES;
+                    const int s = it % NST;
                     unsigned char* a = tiles + s * C::STAGE;
                     if (it >= pre_issued) {             // the first stages are armed and their weights asked for already
-                        if (!mbar_wait(empty + s, ((it / C::STAGES) & 1) ^ 1, abort_flag, status, IK_WAIT_LIMIT_NS, 1, it)) { ok = false; break; }
-                        mbar_expect_tx(full + s, C::STAGE);
+                        if (!mbar_wait(empty + s, ((it / NST) & 1) ^ 1, abort_flag, status, IK_WAIT_LIMIT_NS, 1, it)) { ok = false; break; }
+                        mbar_expect_tx(full + s, stage_bytes);
                         tma_load_2d(a, &map_w, (kb0 + i) * BK, n0, full + s);
                     }
                     tma_load_2d(a + C::A_BYTES, &map_x, (kb0 + i) * BK, m0, full + s);
@@ -217,15 +262,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
             if (*abort_flag) {
                 // leave no copy of this block in flight: wait (bounded) for the stages that were armed last
-                for (int i = max(0, armed - C::STAGES); i < armed; i++) {
+                for (int i = max(0, armed - NST); i < armed; i++) {
                     const long long c0 = wait_clock();
-                    while (!mbar_test(full + i % C::STAGES, (i / C::STAGES) & 1) && !wait_ran_out(c0, 2000000ull)) {}
+                    while (!mbar_test(full + i % NST, (i / NST) & 1) && !wait_ran_out(c0, 2000000ull)) {}
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc(BN);
+            const uint32_t idesc = umma_idesc(bn);
             int it = 0, lt = 0;
             bool ok = true;
             Walk walk = walk_init;
@@ -237,9 +282,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem_base + buf * C::ACC_COLS;
                 for (int i = 0; i < nkb; i++, it++) {
-                    const int s = it % C::STAGES;
-                    ok = mbar_wait(full + s, (it / C::STAGES) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 3, it);
+                    const int s = it % NST;
+                    ok = mbar_wait(full + s, (it / NST) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 3, it);
                     if (!ok) break;
+                    if (it == 0) IK_STAMP(3);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t a = smem_u32(tiles + s * C::STAGE), b = a + C::A_BYTES;
                     #pragma unroll
@@ -248,6 +294,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     umma_commit(empty + s);             // the stage is free once these MMAs have read it
                 }
                 if (ok) umma_commit(acc_full + buf);
+                IK_STAMP(4);
             }
         }
     } else {
@@ -257,7 +304,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         int lt = 0;
         Walk walk = walk_init;
         for (Work w; walk.next(w); lt++) {
-            const int n0 = w.nt * BM, m0 = w.mt * BN, z = w.z;
+            const int n0 = w.nt * BM, m0 = w.mt * bn, z = w.z;
             const int buf = lt & 1;
             // stream-K: a piece that does not hold the tile's first K step is handed over raw; the piece that does
             // hold it gathers the pieces of the blocks after this one, [c_lo, c_hi)
@@ -273,7 +320,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 // each warp keeps its own list of the tile's cache rows (no barrier between warps is needed); the
                 // lookups run while the accumulator is still being filled
                 __syncwarp();
-                for (int i = lane; i < BN; i += 32) rope_rows[quarter][i] = ik_rope_cache_row(rope, m0 + i, M);
+                for (int i = lane; i < bn; i += 32) rope_rows[quarter][i] = ik_rope_cache_row(rope, m0 + i, M);
                 __syncwarp();
             }
             const int row = quarter * 32 + lane;
@@ -292,13 +339,58 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 fetch_piece(c_lo, 0, ahead[0]);
                 fetch_piece(c_lo + 1, 0, ahead[1]);
             }
+            // Adding into Y: what Y holds was written by earlier kernels, so the first 16 columns of it are asked for
+            // before the accumulator is waited for, and each further 16 while the 16 before them are being added.
+            const bool adds_to_y = accumulate && !slice_sums && !swiglu && !fused_rope && !hand_over && !(CL && z > 0);
+            float y_ahead[16];
+            auto load_y = [&](int c0) {
+                #pragma unroll
+                for (int c = 0; c < 16; c++)
+                    y_ahead[c] = (feature < N && m0 + c0 + c < M) ? ik_ld(Y, (size_t)(m0 + c0 + c) * ldy + feature) : 0.f;
+            };
+            if (adds_to_y) load_y(0);
             if (!mbar_wait(acc_full + buf, (lt >> 1) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 4, lt)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * C::ACC_COLS;
+            if (threadIdx.x == 64) IK_STAMP(5);
+            if (CL && z > 0) {
+                // cluster mode, not rank 0: this lane's row of raw sums goes into rank 0's shared memory, then this
+                // thread's arrival on rank 0's barrier releases what it stored
+                const uint32_t theirs = cluster_addr(smem_u32(red + ((size_t)(z - 1) * BN) * BM + row), 0);
+                #pragma unroll 1
+                for (int c0 = 0; c0 < bn && m0 + c0 < M; c0 += 16) {
+                    float v[16];
+                    tmem_ld16(acc + c0, v);
+                    #pragma unroll
+                    for (int c = 0; c < 16; c++) st_cluster_f32(theirs + (uint32_t)(c0 + c) * BM * 4, v[c]);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(acc_empty + buf);
+                mbar_arrive_cluster(cluster_addr(smem_u32(red_full), 0));
+                continue;
+            }
+            if (CL && n_splits > 1) {
+                // rank 0: the other ranks' sums (waited for with the same bound as everything else)
+                const long long c0 = wait_clock();
+                bool there = mbar_test_cluster(red_full, 0);
+                for (int spin = 0; !there; spin++) {
+                    there = mbar_test_cluster(red_full, 0);
+                    if (!there && (spin & 63) == 63) {
+                        if (*abort_flag) break;
+                        if (wait_ran_out(c0, IK_WAIT_LIMIT_NS)) {
+                            note_wait_gave_up(6, lt, 0);
+                            *abort_flag = 1;
+                            ik_set_status(status, IK_STATUS_GEMM_TIMEOUT);
+                            break;
+                        }
+                    }
+                }
+                if (!there) break;
+            }
             if (hand_over) {
                 float* mine = pieces + (size_t)blockIdx.x * BN * BM + row;
                 #pragma unroll 1
-                for (int c0 = 0; c0 < BN && m0 + c0 < M; c0 += 16) {
+                for (int c0 = 0; c0 < bn && m0 + c0 < M; c0 += 16) {
                     float v[16];
                     tmem_ld16(acc + c0, v);
                     #pragma unroll
@@ -316,11 +408,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             // the accumulator's columns c0 .. c0 + 15 of this lane's row, with the other blocks' pieces added in K order
             auto read_sums = [&](int c0, float (&v)[16]) {
                 tmem_ld16(acc + c0, v);
+                if (CL) {                                // the other ranks' sums of these columns, added in rank order
+                    for (int r = 0; r + 1 < n_splits; r++) {
+                        const float* p = red + ((size_t)r * BN + c0) * BM + row;
+                        #pragma unroll
+                        for (int i = 0; i < 16; i++) v[i] += p[(size_t)i * BM];
+                    }
+                    return;
+                }
                 if (c_hi == c_lo) return;
                 float p[16], q[16];
                 #pragma unroll
                 for (int i = 0; i < 16; i++) { p[i] = ahead[0][i]; q[i] = ahead[1][i]; }
-                if (c0 + 16 < BN && m0 + c0 + 16 < M) {
+                if (c0 + 16 < bn && m0 + c0 + 16 < M) {
                     fetch_piece(c_lo, c0 + 16, ahead[0]);
                     fetch_piece(c_lo + 1, c0 + 16, ahead[1]);
                 }
@@ -341,7 +441,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                                   (size_t)(head - rope.nh - (rotated ? 0 : rope.nkv)) * rope.page_size * rope.hd + r0;
             const float2* const cs_base = reinterpret_cast<const float2*>(rope.cos_sin) + (r0 >> 1);
             #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
+            for (int c0 = 0; c0 < bn; c0 += 16) {
                 if (m0 + c0 >= M) break;
                 float v[16];
                 if (fused_rope) {
@@ -400,12 +500,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         }
                     } else {
                         if (accumulate) {
-                            float y[16];
                             #pragma unroll
-                            for (int c = 0; c < 16; c++)
-                                y[c] = m0 + c0 + c < M ? ik_ld(Y, (size_t)(m0 + c0 + c) * ldy + feature) : 0.f;
-                            #pragma unroll
-                            for (int c = 0; c < 16; c++) v[c] += y[c];
+                            for (int c = 0; c < 16; c++) v[c] += y_ahead[c];
+                            if (c0 + 16 < bn && m0 + c0 + 16 < M) load_y(c0 + 16);
                         }
                         #pragma unroll
                         for (int c = 0; c < 16; c++)
@@ -422,12 +519,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
         }
     }
+    if (threadIdx.x == 64) IK_STAMP(6);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
     }
+    if (threadIdx.x == 0) IK_STAMP(7);
+    // no block of a cluster leaves while another may still store into its shared memory or arrive on its barrier
+    if (CL) cluster_sync();
 }
 
 // Adds the K slices in slice order and writes Y.
@@ -474,20 +575,51 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TY* __re
     }
 }
 
+// Cluster mode: n_cl blocks per tile, each a slice of K, summed in rank 0's shared memory.
+template <int BN, typename TY>
+int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int M, int N, int K, int ldy, int accumulate,
+                   int swiglu, int n_cl, int* status, const IkRopeStore& rope, int bn, cudaStream_t stream) {
+    typedef Cfg<BN> C;
+    if (C::RED_SLOTS == 0) return IK_UNSUPPORTED;
+    const int nkb = (K + BK - 1) / BK;
+    const long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
+    const int per = (nkb + n_cl - 1) / n_cl;
+    if (n_cl < 2 || n_cl > C::RED_SLOTS + 1 || (long long)(n_cl - 1) * per >= nkb || tiles * n_cl > max_blocks()) return IK_UNSUPPORTED;
+    auto kern = gemm_tcgen05_kernel<BN, TY, true>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::CL_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(tiles * n_cl));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = C::CL_SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = n_cl; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (ik_pdl_mask() & IK_FAMILY) ? 2 : 1;
+    IK_RETURN_IF_ERROR(cudaLaunchKernelEx(&cfg, kern, mw, mx, (TY*)Y, (float*)nullptr, M, N, K, ldy, accumulate, swiglu, per, n_cl, 0,
+                                          status, rope, bn));
+    return (int)cudaGetLastError();
+}
+
 template <int BN, typename TY>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial, int M, int N, int K, int ldy,
-           int accumulate, int swiglu, int splits, int* status, const IkRopeStore& rope, cudaStream_t stream) {
+           int accumulate, int swiglu, int splits, int* status, const IkRopeStore& rope, int bn, cudaStream_t stream) {
     typedef Cfg<BN> C;
-    auto kern = gemm_tcgen05_kernel<BN, TY>;
+    if (splits < 0) return launch_cluster<BN, TY>(mw, mx, Y, M, N, K, ldy, accumulate, swiglu, -splits, status, rope, bn, stream);
+    auto kern = gemm_tcgen05_kernel<BN, TY, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
     if (e != cudaSuccess) return (int)e;
     const int nkb = (K + BK - 1) / BK;
-    const long long tiles = (long long)((N + BM - 1) / BM) * ((M + BN - 1) / BN);
+    const long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
     if (splits == 0) {                  // stream-K: equal shares of all (tile, K step) units, at least four K steps a block
         const long long units = tiles * nkb;
         const int blocks = (int)(units / 4 < 1 ? 1 : units / 4 < max_blocks() ? units / 4 : max_blocks());
         IK_RETURN_IF_ERROR(ik_launch(kern, blocks, THREADS, C::SMEM, stream, mw, mx, (TY*)Y, partial, M, N, K, ldy, accumulate,
-                                     swiglu, nkb, 1, 1, status, rope));
+                                     swiglu, nkb, 1, 1, status, rope, bn));
         return (int)cudaGetLastError();
     }
     const int per = (nkb + splits - 1) / splits;
@@ -495,7 +627,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial
     const long long total = tiles * n_splits;
     const int blocks = (int)(total < max_blocks() ? total : max_blocks());
     IK_RETURN_IF_ERROR(ik_launch(kern, blocks, THREADS, C::SMEM, stream, mw, mx, (TY*)Y, n_splits > 1 ? partial : nullptr, M,
-                                 N, K, ldy, accumulate, swiglu, per, n_splits, 0, status, rope));
+                                 N, K, ldy, accumulate, swiglu, per, n_splits, 0, status, rope, bn));
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (n_splits > 1) {
@@ -511,36 +643,55 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial
 
 }  // namespace
 
-// Token-tile width the kernel will use for M tokens.
+// The room a token tile has for M tokens (the kernel's variant): 32, 64, 128 or 256 tokens.
 IK_EXPORT int ik_gemm_tcgen05_tile(int M) { return M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
+
+// The width of token tile in use for M tokens and N output features: a multiple of 16 up to the room.  Up to 256
+// tokens: the tokens rounded up.  Beyond: of the widths from 192 to 256, the one with which the tiles fill the rounds
+// of the persistent grid best (a round costs about as much as the bytes a block loads per K step, 128 + width rows):
+// 2,048 tokens and 4,096 features are 256 tiles of 256 (two rounds on 148 SMs, the second 73 % full) or 288 tiles of 240.
+IK_EXPORT int ik_gemm_tcgen05_tile_width(int M, int N) {
+    if (M <= 256) return M <= 16 ? 16 : (M + 15) / 16 * 16;
+    const long long tiles_n = (N + BM - 1) / BM, sms = max_blocks();
+    int best = 256;
+    long long best_cost = -1;
+    for (int bn = 256; bn >= 192; bn -= 16) {
+        const long long rounds = (tiles_n * ((M + bn - 1) / bn) + sms - 1) / sms;
+        const long long cost = rounds * (bn + BM);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
 
 // Scratch of the stream-K mode, in bytes: zeroed once by the caller, then left to the kernels (one stream at a time).
 IK_EXPORT int ik_gemm_tcgen05_stream_k_bytes() { return (int)stream_k_bytes(); }
 
 // splits > 1 needs `partial`: splits * M * N floats of scratch owned by the caller.
 // splits == 0 is the stream-K mode; `partial` is then the scratch described above.
+// splits < 0 is the cluster mode with -splits blocks per tile (2 to 4 for up to 64 tokens, 2 for up to 128); it needs
+// no scratch, and returns IK_UNSUPPORTED where it does not apply (more tokens, more tiles than SMs, too few K steps).
 // status: device int; set to 4 if a block gave up waiting (the result is then not to be used).
 // swiglu: W holds (gate j, up j) in rows (2j, 2j + 1); Y is [M, N / 2] = silu(gate) * up.
 static int gemm_tcgen05_impl(const void* X, const void* W, void* Y, int y_dtype, float* partial, int M, int N, int K,
                              int ldx, int ldw, int ldy, int accumulate, int swiglu, int splits, int* status,
                              const IkRopeStore& rope, cudaStream_t stream) {
-    if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || (!rope.q_out && ldy < (swiglu ? N / 2 : N)) || splits < 0)
+    if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || (!rope.q_out && ldy < (swiglu ? N / 2 : N)))
         return IK_BAD_ARGUMENT;
     if (swiglu && ((N & 1) || accumulate)) return IK_BAD_ARGUMENT;
     if (y_dtype != IK_F32 && y_dtype != IK_BF16) return IK_BAD_ARGUMENT;
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return IK_UNSUPPORTED;
-    if (splits != 1 && !partial) return IK_BAD_ARGUMENT;
+    if (splits != 1 && splits >= 0 && !partial) return IK_BAD_ARGUMENT;
     if (M == 0) return IK_OK;
-    const int bn = ik_gemm_tcgen05_tile(M);
+    const int room = ik_gemm_tcgen05_tile(M), bn = ik_gemm_tcgen05_tile_width(M, N);
     CUtensorMap mw, mx;
     int st = ik_make_map(&mw, W, N, K, ldw, BM);
     if (st != IK_OK) return st;
     st = ik_make_map(&mx, X, M, K, ldx, bn);
     if (st != IK_OK) return st;
 #define IK_TC(BN_)                                                                                                       \
-    return y_dtype == IK_F32 ? launch<BN_, float>(mw, mx, Y, partial, M, N, K, ldy, accumulate, swiglu, splits, status, rope, stream) \
-                             : launch<BN_, bf16>(mw, mx, Y, partial, M, N, K, ldy, accumulate, swiglu, splits, status, rope, stream)
-    switch (bn) {
+    return y_dtype == IK_F32 ? launch<BN_, float>(mw, mx, Y, partial, M, N, K, ldy, accumulate, swiglu, splits, status, rope, bn, stream) \
+                             : launch<BN_, bf16>(mw, mx, Y, partial, M, N, K, ldy, accumulate, swiglu, splits, status, rope, bn, stream)
+    switch (room) {
         case 32: IK_TC(32);
         case 64: IK_TC(64);
         case 128: IK_TC(128);
@@ -610,3 +761,13 @@ IK_EXPORT int ik_selftest_wait_expires(int* status, int* result, const int* neve
     wait_expiry_kernel<<<1, 96, 0, stream>>>(status, result, never_set, limit_ns);
     IK_LAUNCH_STATUS();
 }
+
+#ifdef IK_TIMELINE
+IK_EXPORT int ik_gemm_tcgen05_timeline(unsigned long long* out /* [1024][8] */) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, ik_timeline, sizeof(unsigned long long) * 1024 * 8);
+    if (e != cudaSuccess) return (int)e;
+    static unsigned long long zeros[1024 * 8];
+    e = cudaMemcpyToSymbol(ik_timeline, zeros, sizeof(zeros));
+    return e == cudaSuccess ? IK_OK : (int)e;
+}
+#endif

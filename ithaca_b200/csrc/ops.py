@@ -78,6 +78,7 @@ _SIGNATURES = {
     "ik_gemm_bf16_mma": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "ik_gemm_tcgen05": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_gemm_tcgen05_tile": [_i],
+    "ik_gemm_tcgen05_tile_width": [_i, _i],
     "ik_gemm_tcgen05_stream_k_bytes": [],
     "ik_rope_table": [_vp, _vp, _vp, _i, _i, _vp],
     "ik_gemm_qkv_rope_mma": [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
@@ -369,19 +370,36 @@ def stream_k_scratch(device) -> torch.Tensor:
     return t
 
 
+def tcgen05_cluster_fits(M: int, N: int, K: int, n_cl: int) -> bool:
+    """Whether the cluster mode of the tcgen05 product takes this shape with ``n_cl`` blocks per tile."""
+    tile_m = lib().ik_gemm_tcgen05_tile(M)
+    tiles = -(-N // 128) * -(-M // tile_m)
+    steps = -(-K // 64)
+    most = 4 if tile_m <= 64 else 2 if tile_m <= 128 else 1
+    return 2 <= n_cl <= most and tiles * n_cl <= sm_count() and (n_cl - 1) * -(-steps // n_cl) < steps
+
+
 def tcgen05_splits(M: int, N: int, K: int) -> int:
     """How the tcgen05 product shares out its work: 1 = whole tiles dealt round robin; n > 1 = n slices
-    of K and a second kernel that adds them; 0 = stream-K (equal shares of all K steps of all tiles).
-    Measured on B200 with 4096 x 4096 .. 28672 x 4096 weights: with fewer tiles than half the SMs, K
-    slices win; stream-K wins when whole tiles would leave more than a tenth of the SMs' time unused
-    and there is one token tile of at most 128 tokens (bandwidth-bound); beyond that whole tiles win."""
+    of K and a second kernel that adds them; 0 = stream-K (equal shares of all K steps of all tiles);
+    -n = clusters of n blocks per tile, each a slice of K, summed in shared memory (no scratch, one kernel).
+    Measured on B200 with 2048 x 2048 .. 28672 x 4096 weights (``bench.py --only products --tokens ...``): with
+    fewer tiles than half the SMs, K is sliced: by clusters of 2 or 4 where that busies at least half the SMs (clusters
+    of 3 measured far slower), else by a second kernel; stream-K wins when whole tiles would leave more than a
+    tenth of the SMs' time unused and there is one token tile of at most 128 tokens (bandwidth-bound); beyond that
+    whole tiles win."""
     N_SM = sm_count()
     tile_m = lib().ik_gemm_tcgen05_tile(M)
-    tiles_m = -(-M // tile_m)
+    tiles_m = -(-M // lib().ik_gemm_tcgen05_tile_width(M, N))
     tiles = -(-N // 128) * tiles_m
     steps = -(-K // 64)
     if 2 * tiles <= N_SM:
-        return max(1, min(N_SM // tiles, steps // 4))
+        want = max(1, min(N_SM // tiles, steps // 4))
+        most = 4 if tile_m <= 64 else 2 if tile_m <= 128 else 1
+        n_cl = 4 if want >= 4 and most >= 4 else 2 if want >= 2 and most >= 2 else 0
+        if n_cl and 2 * tiles * n_cl >= N_SM and tcgen05_cluster_fits(M, N, K, n_cl):
+            return -n_cl
+        return want
     rounds = -(-tiles // N_SM)
     if tiles_m == 1 and tile_m <= 128 and tiles / (rounds * N_SM) < 0.9 and tiles * steps >= 8:
         return 0
@@ -447,7 +465,7 @@ def rope_table(token_pos: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
 def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                   cos_sin: torch.Tensor, token_seq: torch.Tensor, token_pos: torch.Tensor, table: torch.Tensor,
                   n_heads: int, n_kv_heads: int, head_dim: int, write_cache: bool, status: Optional[torch.Tensor],
-                  skinny_max: int = 16) -> bool:
+                  skinny_max: int = 16, splits: Optional[int] = None) -> bool:
     """q, k, v = x W^T with rotary pairs in adjacent rows of W; rotated q to ``q_out``, rotated k and v into
     the pages.  Returns False when the kernels do not take these sizes (the caller then runs the steps apart)."""
     _need(x, "x", torch.bfloat16, contiguous=False)
@@ -474,7 +492,8 @@ def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages
         st = lib().ik_gemm_qkv_rope_mma(_ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), ctypes.byref(rs), _stream())
         kernels = 1
     else:
-        splits = tcgen05_splits(M, N, K)
+        if splits is None:
+            splits = tcgen05_splits(M, N, K)
         partial = (stream_k_scratch(x.device) if splits == 0 else
                    torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None)
         st = lib().ik_gemm_qkv_rope_tcgen05(_ptr(x), _ptr(w), _ptr(partial), M, N, K, x.stride(0), w.stride(0), splits,

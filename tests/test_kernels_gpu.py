@@ -128,6 +128,39 @@ def test_gemm_tcgen05(M, N, K, splits, ydt):
     close(got, ref + base.double(), 2e-5 if ydt == torch.float32 else 8e-3)
 
 
+@pytest.mark.parametrize("M,N,K,n_cl", [(17, 4096, 512, 2), (17, 4096, 512, 4), (64, 384, 2048, 3), (33, 130, 328, 3),
+                                        (100, 96, 264, 2), (128, 4096, 1024, 2), (1, 200, 4096, 4), (64, 6000, 4096, 3)])
+@pytest.mark.parametrize("ydt", [torch.float32, torch.bfloat16])
+def test_gemm_tcgen05_cluster_mode(M, N, K, n_cl, ydt):
+    """Few tiles: clusters of 2 to 4 blocks share a tile, each a slice of K, and the block of rank 0 adds the
+    others' sums from its shared memory in rank order.  Plain, accumulating, the same bits every time; and the
+    shapes the mode does not take are refused, not computed."""
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert ops().tcgen05_cluster_fits(M, N, K, n_cl)
+    x, w = rnd((M, K), 26, torch.bfloat16).to(DEV), rnd((N, K), 27, torch.bfloat16).to(DEV)
+    ref = x.double().cpu() @ w.double().cpu().T
+    got = ops().gemm_tcgen05(x, w, out_dtype=ydt, splits=-n_cl, status=status)
+    assert got is not None and status.item() == 0
+    close(got, ref, 2e-5 if ydt == torch.float32 else 5e-3)
+    for _ in range(3):
+        assert torch.equal(ops().gemm_tcgen05(x, w, out_dtype=ydt, splits=-n_cl, status=status), got)
+    base = rnd((M, N), 28, ydt)
+    acc = ops().gemm_tcgen05(x, w, out=base.to(DEV).clone(), accumulate=True, splits=-n_cl, status=status)
+    close(acc, ref + base.double(), 2e-5 if ydt == torch.float32 else 8e-3)
+    assert status.item() == 0
+
+
+def test_gemm_tcgen05_cluster_mode_refuses_what_it_does_not_take():
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for M, N, K, n_cl in [(300, 256, 512, 2), (100, 256, 512, 3), (17, 128 * 80, 512, 2), (17, 256, 64, 2), (17, 256, 512, 5)]:
+        assert not ops().tcgen05_cluster_fits(M, N, K, n_cl)
+        x, w = rnd((M, K), 1, torch.bfloat16).to(DEV), rnd((N, K), 2, torch.bfloat16).to(DEV)
+        out = torch.full((M, N), 3.0, device=DEV)
+        assert ops().gemm_tcgen05(x, w, out=out, splits=-n_cl, status=status) is None
+        assert float(out.min()) == 3.0 and float(out.max()) == 3.0
+    assert status.item() == 0
+
+
 def test_gemm_tcgen05_stream_k_back_to_back():
     """Stream-K products of different shapes one after another share one scratch: every launch leaves the
     flags as it found them, a tile cut into many pieces (one tile, K = 8192) sums them in K order, and the
@@ -177,7 +210,9 @@ def test_gate_up_product_with_swiglu_epilogue(M, ff, d):
     close(got, ref, 6e-3)
     status = ops().device_status(DEV)
     if M > 8:                                            # 9-16 tokens go to either kernel, by the matrix's size
-        for splits in (1, 3, 0):
+        for splits in (1, 3, 0, -2):
+            if splits < 0 and not ops().tcgen05_cluster_fits(M, 2 * ff, d, -splits):
+                continue
             got = ops().gemm_tcgen05(x.to(DEV), wi, out_dtype=torch.float32, splits=min(splits, -(-d // 64)), status=status,
                                      swiglu=True)
             close(got, ref, 2e-5)
@@ -266,7 +301,7 @@ def test_rope_append(nh, nkv, hd, rot, pairing, dtype):
 
 
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 4, 16), (6, 2, 32), (5, 1, 48), (8, 2, 128)])
-@pytest.mark.parametrize("T_new", [[3, 5, 1], [40, 30, 66], [300, 2, 70]])
+@pytest.mark.parametrize("T_new", [[3, 5, 1], [20, 7, 30], [40, 30, 66], [300, 2, 70]])
 def test_qkv_product_with_rotary_and_cache_epilogue(nh, nkv, hd, T_new):
     """x W^T, rotated, with q to its buffer and k, v into the pages, from one kernel: every dispatch path
     (skinny, tcgen05 with whole tiles and stream-K) against the plain product followed by the plain rotation."""
@@ -307,6 +342,16 @@ def test_qkv_product_with_rotary_and_cache_epilogue(nh, nkv, hd, T_new):
     for s, p in zip(token_seq, token_pos):
         touched[pg.table[s, p // 64], p % 64] = True
     assert k_h.float().abs().sum(dim=(1, 3))[~touched].max().item() == 0 and v_h.float().abs().sum(dim=(1, 3))[~touched].max().item() == 0
+    # the cluster mode of the tcgen05 product through the same epilogue
+    N_all = (nh + 2 * nkv) * hd
+    if T > 16 and ops().tcgen05_cluster_fits(T, N_all, d, 2):
+        q3, (k3, v3, _) = torch.zeros_like(q_out), pg.dev()
+        assert ops().gemm_qkv_rope(x.to(DEV), w, q3, k3, v3, cs, torch.from_numpy(token_seq).to(DEV), pos.to(DEV), tab,
+                                   nh, nkv, hd, True, status, splits=-2)
+        close(q3.view(T, nh, hd), q_ref[:, :, order], 6e-3)
+        k3h = k3.cpu()
+        close(torch.stack([k3h[pg.table[s, p // 64], :, p % 64] for s, p in zip(token_seq, token_pos)]), k_ref[:, :, order], 6e-3)
+        assert status.item() == 0
     # without the right to write the cache only q appears
     k2, v2 = torch.zeros_like(k_d), torch.zeros_like(v_d)
     assert ops().gemm_qkv_rope(x.to(DEV), w, q_out, k2, v2, cs, torch.from_numpy(token_seq).to(DEV), pos.to(DEV), tab,
