@@ -231,8 +231,11 @@ def long_13b_run(pk):
     rng = np.random.default_rng(6)
     eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=batch * (final + 64), max_slots=batch, ctx=final + 64)
     opts = dict(temp=0.0, rep_pen=1.0, stop_token_ids=[])
-    # warm-up: a short run at each width of block table the long run will meet (16 to 32, and 33 to 64 pages)
-    for n in (prompt_len, 2048 + 8):
+    # warm-up: a short run at each width of block table the long run will meet, so that its graphs exist
+    from ithaca_b200.engine.graph import _bucket
+    widths = sorted({_bucket(c) for c in range(prompt_len // 64 + 1, final // 64 + 1)})
+    for w in widths:
+        n = min(final - 8, max(prompt_len, (w - 1) * 64 + 8))
         eng.generate([rng.integers(0, vocab, size=n).tolist() for _ in range(batch)], max_tokens=4, **opts)
     prompts = [rng.integers(0, vocab, size=prompt_len).tolist() for _ in range(batch)]
     stamps = []
@@ -417,6 +420,25 @@ def attention_run(cfg, reps):
     return out
 
 
+def attempt(run, eng=None):
+    """One part of the line: run it, once more if it raises, and if it raises again say so in its place.  The other
+    parts of the line stand on their own measurements and are printed all the same."""
+    last = None
+    for _ in range(2):
+        try:
+            return run()
+        except Exception as e:                             # noqa: BLE001  (whatever it is goes into the line)
+            last = e
+            import torch
+            torch.cuda.synchronize()
+            if eng is not None:
+                eng.runtime.status.zero_()
+                for s in range(eng.cache.max_slots):
+                    if eng.cache.table.in_use(s):
+                        eng.free_slot(s)
+    return {"error": f"{type(last).__name__}: {last}"[:300]}
+
+
 def model_flops_per_token(cfg, n_layers):
     d, ff, nh, nkv, hd, V = (cfg["hidden_size"], cfg["intermediate_size"], cfg["num_attention_heads"],
                              cfg["num_key_value_heads"], cfg["head_dim"], cfg["vocab_size"])
@@ -500,8 +522,12 @@ def main():
     points = {}
     if point_batches:
         for b in point_batches:
-            points[f"decode_b{b}"] = round(decode_run(eng, b, min(args.steps, 32), args.warmup, vocab, CONTEXT)["tok_s"], 1)
-    e2e = e2e_run(eng, args.batch, E2E_STEPS, vocab, CONTEXT)
+            r = attempt(lambda: decode_run(eng, b, min(args.steps, 32), args.warmup, vocab, CONTEXT), eng)
+            if "error" in r:
+                points[f"decode_b{b}_error"] = r["error"]
+            else:
+                points[f"decode_b{b}"] = round(r["tok_s"], 1)
+    e2e = attempt(lambda: e2e_run(eng, args.batch, E2E_STEPS, vocab, CONTEXT), eng)
     pre_ms = prefill_run(eng, PREFILL_TOKENS, vocab)
 
     layer_flops, head_flops = model_flops_per_token(cfg, n_layers)
@@ -522,9 +548,9 @@ def main():
                    "seq_len": CONTEXT, "parallelism": "single GPU", "l2": "inputs larger than L2 (weights + cache)",
                    "cache_page": 64, "peaks": pk["source"]},
         "clocks": main_run["clocks"],
-        "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tok/s", "h2d_bytes_per_step": e2e["h2d"],
-                "d2h_bytes_per_step": e2e["d2h"], "steps": e2e["steps"], "first32_tok_s": round(e2e["first32_tok_s"], 1),
-                "settled_tok_s": round(e2e["settled_tok_s"], 1)},
+        "e2e": ({"value": round(e2e["tok_s"], 1), "unit": "tok/s", "h2d_bytes_per_step": e2e["h2d"],
+                 "d2h_bytes_per_step": e2e["d2h"], "steps": e2e["steps"], "first32_tok_s": round(e2e["first32_tok_s"], 1),
+                 "settled_tok_s": round(e2e["settled_tok_s"], 1)} if "error" not in e2e else e2e),
         "gpu_launches": main_run["launches_per_step"] * args.steps,
         "prefill": {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
                     "frac": round(pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
@@ -535,8 +561,8 @@ def main():
     if not args.no_points and args.shape == "8b" and not args.layers:
         del eng
         torch.cuda.empty_cache()
-        points["1b_unequal"] = unequal_1b_run(pk)
-        points["13b_long"] = long_13b_run(pk)
+        points["1b_unequal"] = attempt(lambda: unequal_1b_run(pk))
+        points["13b_long"] = attempt(lambda: long_13b_run(pk))
     print(json.dumps(line))
     return 0
 

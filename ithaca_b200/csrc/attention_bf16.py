@@ -130,7 +130,8 @@ def attend(q, k_pages, v_pages, ctx, table, n_heads: int, scale: float, window: 
         keys = sum(min(e, window + n) if window else e for n, e in zip(ctx.host_n_new, ctx.host_kv_lens))
         work = (2 * q.numel() * 2 + 2 * keys * nkv * hd * 2, 4 * hd * n_heads * pairs)
     if ctx.is_decode:
-        chunk = decode_chunk_pages(ctx.n_seqs, n_heads, nkv, ctx.max_kv_len, page_size)
+        # from the bound, not from this step's longest sequence: a captured graph is replayed for other lengths
+        chunk = decode_chunk_pages(ctx.n_seqs, n_heads, nkv, ctx.kv_len_bound, page_size)
         return decode(q, k_pages, v_pages, ctx.kv_lens, table, ctx.n_seqs, ctx.kv_len_bound, n_heads, scale, window,
                       status, chunk_pages=chunk, work=work)
     return prefill(q, k_pages, v_pages, ctx.cu_seqlens, ctx.kv_lens, table, ctx.n_seqs, ctx.max_new, n_heads, scale,

@@ -65,11 +65,15 @@ class _Launched:
 
 
 def _bucket(cols: int) -> int:
-    """Block-table widths are rounded up so that a growing sequence re-captures rarely."""
-    b = 4
-    while b < cols:
-        b *= 2
-    return b
+    """Block-table widths are rounded up so that a growing sequence re-captures rarely: to multiples of 4 up to 32,
+    then in four steps per doubling (40, 48, 56, 64, 80, ...).  What a captured step derives from the length of its
+    longest sequence (grid sizes, the chunk length of decode attention) it derives from the width's upper end, so
+    beyond 1,024 positions no graph is replayed for a longest sequence shorter than four fifths of what it was shaped for."""
+    p = 4
+    while 2 * p < cols:
+        p *= 2
+    step = max(4, p // 4)                     # cols lies in (p, 2p] (or is at most 8)
+    return -(-cols // step) * step
 
 
 class GraphDecoder:
