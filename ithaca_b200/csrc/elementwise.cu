@@ -357,13 +357,14 @@ IK_EXPORT int ik_device_sm_count() { return ik_sm_count(); }
 // dst[i] = src[i] over n 16-byte words: the plain streaming copy that the bandwidth figure of the peaks'
 // self-measurement stands on (read + write bytes over its time).
 __global__ void __launch_bounds__(256) copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x * 4;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x * 4 + threadIdx.x; i < n; i += stride) {
-        uint4 v[4];
+    constexpr int U = 8;                                   // 128 bytes a thread in flight
+    const size_t stride = (size_t)gridDim.x * blockDim.x * U;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x * U + threadIdx.x; i < n; i += stride) {
+        uint4 v[U];
         #pragma unroll
-        for (int j = 0; j < 4; j++) if (i + (size_t)j * blockDim.x < n) v[j] = __ldcs(src + i + (size_t)j * blockDim.x);
+        for (int j = 0; j < U; j++) if (i + (size_t)j * blockDim.x < n) v[j] = __ldcs(src + i + (size_t)j * blockDim.x);
         #pragma unroll
-        for (int j = 0; j < 4; j++) if (i + (size_t)j * blockDim.x < n) __stcs(dst + i + (size_t)j * blockDim.x, v[j]);
+        for (int j = 0; j < U; j++) if (i + (size_t)j * blockDim.x < n) __stcs(dst + i + (size_t)j * blockDim.x, v[j]);
     }
 }
 
@@ -371,7 +372,7 @@ IK_EXPORT int ik_copy(const void* src, void* dst, unsigned long long bytes, cuda
     if (bytes % 16 || ((uintptr_t)src % 16) || ((uintptr_t)dst % 16)) return IK_BAD_ARGUMENT;
     if (bytes == 0) return IK_OK;
     const size_t n = bytes / 16;
-    const size_t want = (n + 1023) / 1024, cap = (size_t)ik_sm_count() * 8;
+    const size_t want = (n + 2047) / 2048, cap = (size_t)ik_sm_count() * 8;
     copy_kernel<<<(int)(want < cap ? want : cap), 256, 0, stream>>>((const uint4*)src, (uint4*)dst, n);
     IK_LAUNCH_STATUS();
 }

@@ -59,6 +59,7 @@ def profile_step(engine, slots: Sequence[int], tokens: Sequence[Sequence[int]], 
     kernel call and shape, in order of first appearance, the number of calls, their time, and the bytes and
     operations they had to move and do."""
     engine._settle()
+    ops.argmax_scratch(engine.runtime.device)             # made now if it is not there yet, not inside the timed calls
     torch.cuda.synchronize()
     with ops.Profile() as prof:
         logits = engine.stepper.step(slots, tokens, want)
@@ -85,4 +86,6 @@ def format_table(rows: List[dict], peaks: Optional[Dict[str, float]] = None, tit
             frac = f"{f:9.2f}" if r["bytes"] or r["flops"] else ""
         lines.append(f"{r['kernel']:<44}{r['calls']:>6}{r['us']:>11.1f}{r['us'] / total:>8.1%}{gbs:>9.0f}{tfl:>9.1f}{frac}")
     lines.append(f"{'all kernel calls, one after another':<44}{sum(r['calls'] for r in rows):>6}{total:>11.1f}")
+    lines.append("(each call timed alone between two events, with the host's gaps between calls: the device clocks lower than "
+                 "under a replayed graph, and nothing overlaps; compare shares)")
     return "\n".join(lines)
