@@ -72,6 +72,7 @@ def _build_dir() -> str:
 
 
 def _hash(sources: Sequence[str], defines: Sequence[str]) -> str:
+    """Of every header of the folder, the given sources (listed ones and those they include) and the flags."""
     h = hashlib.sha256()
     for name in sorted(os.listdir(_HERE)):
         if name.endswith((".cuh", ".h")):
@@ -91,9 +92,10 @@ def _run(cmd: List[str], what: str) -> None:
 
 
 def build_library(name: str, sources: Sequence[str], defines: Sequence[str] = (), extra_flags: Sequence[str] = (),
-                  libs: Sequence[str] = ()) -> str:
-    """Builds (if needed) and returns the path of ``lib<name>_<hash>.so``."""
-    tag = _hash(sources, list(defines) + list(extra_flags))
+                  libs: Sequence[str] = (), includes: Sequence[str] = ()) -> str:
+    """Builds (if needed) and returns the path of ``lib<name>_<hash>.so``.  ``includes``: sources that the
+    listed ones include (not compiled on their own, but a change to them is a change to the library)."""
+    tag = _hash(list(sources) + list(includes), list(defines) + list(extra_flags))
     out_dir = _build_dir()
     so = os.path.join(out_dir, f"lib{name}_{tag}.so")
     if os.path.isfile(so):
@@ -131,12 +133,12 @@ def build_library(name: str, sources: Sequence[str], defines: Sequence[str] = ()
 
 
 def load_library(name: str, sources: Sequence[str], defines: Sequence[str] = (), extra_flags: Sequence[str] = (),
-                 libs: Sequence[str] = ()) -> ctypes.CDLL:
+                 libs: Sequence[str] = (), includes: Sequence[str] = ()) -> ctypes.CDLL:
     key = name + "|" + ",".join(defines)
     with _lock:
         lib = _loaded.get(key)
         if lib is None:
-            so = build_library(name, sources, defines, extra_flags, libs)
+            so = build_library(name, sources, defines, extra_flags, libs, includes)
             try:
                 lib = ctypes.CDLL(so)
             except OSError as e:
@@ -152,9 +154,22 @@ def core() -> ctypes.CDLL:
 ATTENTION_HEAD_SIZES = (16, 32, 48, 64, 128)     # the sizes the tests and the benchmark use; others compile on demand
 
 
+PAIRS_SOURCE = "gemm_tcgen05_mc.cu"        # the pair mode of the tcgen05 product: a library of its own, optional
+
+
+def pairs_available() -> bool:
+    return os.path.isfile(os.path.join(_HERE, PAIRS_SOURCE))
+
+
+def pairs() -> ctypes.CDLL:
+    return load_library("ithaca_gemm_pairs", [PAIRS_SOURCE], includes=["gemm_tcgen05.cu"])
+
+
 def build_all() -> None:
-    """Everything that can be compiled ahead of time: the core library and the attention module of
-    every usual head size."""
+    """Everything that can be compiled ahead of time: the core library, the attention module of
+    every usual head size, and the pair mode of the tcgen05 product where its source is there."""
     core()
     for hd in ATTENTION_HEAD_SIZES:
         build_library(f"ithaca_attn_hd{hd}", ["attention_bf16.cu"], defines=[f"IK_HD={hd}"])
+    if pairs_available():
+        build_library("ithaca_gemm_pairs", [PAIRS_SOURCE], includes=["gemm_tcgen05.cu"])

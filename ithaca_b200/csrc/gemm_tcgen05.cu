@@ -33,14 +33,31 @@
 // shared memory) and arrive on a barrier there; rank 0 adds them to its own in rank order and runs the epilogue.
 // No partial sums go through global memory and no second kernel runs.
 //
+// Many tiles (prefill): pairs of blocks (clusters of 2) can take two weight tiles that meet the same token tile and
+// load that token tile once between them: each block fetches half of its rows and the copy lands in both blocks'
+// shared memory.  A stage may then be refilled only when both blocks' products have read it, so the "empty" barriers
+// count two arrivals and each block's commit arrives on both.  This file only says where the paired copy and the
+// paired commit go; the two instructions live in gemm_tcgen05_mc.cu, which includes this file, and without that
+// file the library is built and runs without the mode.
+//
 // Every wait on an mbarrier is bounded: after about a second without progress the waiting
 // thread sets the status word to IK_STATUS_GEMM_TIMEOUT, raises the block's abort flag and
 // every role leaves its loop; TMEM is freed and the block returns.  Blocks that start after
 // the status word is set return at once.  Needs K % 8 == 0 and 16-byte aligned rows (TMA
 // strides); the host entry returns IK_UNSUPPORTED otherwise.
+#ifndef IK_FAMILY
 #define IK_FAMILY 8
+#endif
 #include "tc_common.cuh"
 #include "rope_store.cuh"
+
+#ifndef IK_TCGEN05_PAIRS
+namespace {
+// Stand-ins of the two paired instructions for the build without them (the pair mode is then never launched).
+__device__ __forceinline__ void tma_load_2d_pair(void*, const CUtensorMap*, int, int, uint64_t*) {}
+__device__ __forceinline__ void umma_commit_pair(uint64_t*) {}
+}  // namespace
+#endif
 
 namespace {
 
@@ -79,6 +96,7 @@ struct Work {
 // The sequence of Work of one block.  Every role of the block walks it on its own.
 struct Walk {
     bool sk, cl = false, cl_done = false;   // cl: one piece of work per block: tile blockIdx.x / n_splits, K slice = rank in the cluster
+    bool pairs = false;                     // pairs: block 2c + r takes weight tile 2 * (item / tiles_m) + r of the items c, c + grid / 2, ...
     int tiles_m, tiles_n, nkb_total, kb_per_split;
     int item, n_items;                // data-parallel: items blockIdx.x, + gridDim.x, ...; item -> (K slice, weight tile, token tile)
     long long u, u_end, n_units;      // stream-K: this block's share [u, u_end) of all (tile, K step) units, token tile fastest
@@ -90,6 +108,16 @@ struct Walk {
     }
     __device__ long long share_begin(int block) const { return n_units * block / gridDim.x; }
     __device__ bool next(Work& w) {
+        if (pairs) {
+            if (item >= (tiles_n + 1) / 2 * tiles_m) return false;
+            w.mt = item % tiles_m;
+            w.nt = 2 * (item / tiles_m) + (int)(blockIdx.x & 1);     // may lie past the last weight tile: all zeros, nothing stored
+            w.tile = w.nt * tiles_m + w.mt;
+            w.z = 0; w.kb0 = 0; w.nkb = nkb_total;
+            w.first = w.last = true;
+            item += gridDim.x / 2;
+            return true;
+        }
         if (cl) {
             if (cl_done) return false;
             cl_done = true;
@@ -169,8 +197,9 @@ __device__ unsigned long long ik_timeline[1024][8];
 // that order, so they run at the same time on different SMs and the weight tile is fetched from
 // HBM once.  The accumulator is double-buffered in TMEM: while the epilogue warps drain tile i,
 // the MMA warp already fills the other buffer with tile i + 1.
-// CL: the cluster mode described at the top (n_splits blocks per tile, partial == nullptr, one piece of work per block).
-template <int BN, typename TY, bool CL>
+// MODE 1 (CL): the cluster mode described at the top (n_splits blocks per tile, partial == nullptr, one piece of work
+// per block).  MODE 2 (PAIRS): pairs of blocks share the token tile's copy (whole tiles only; map_x's box is half a tile).
+template <int BN, typename TY, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     TY* __restrict__ Y, float* __restrict__ partial, int M, int N, int K, int ldy, int accumulate,
@@ -178,11 +207,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // bn <= BN: the width of a token tile in use (a multiple of 16): tiles lie bn tokens apart, bn rows of tokens are
     // loaded per stage and the products are bn columns wide; BN is the room a stage and an accumulator have.
     typedef Cfg<BN> C;
+    constexpr bool CL = MODE == 1, PAIRS = MODE == 2;
     extern __shared__ unsigned char smem_raw[];
     __shared__ int rope_rows[4][BN];                   // per epilogue warp: the cache row of each of the tile's tokens
     if (threadIdx.x == 0) IK_STAMP(0);
     // (in cluster mode every block goes on to the cluster's barrier below; its waits are bounded all the same)
-    if (!CL && ik_status_has(status, IK_STATUS_GEMM_TIMEOUT)) return;     // an earlier block gave up
+    if (!CL && !PAIRS && ik_status_has(status, IK_STATUS_GEMM_TIMEOUT)) return;     // an earlier block gave up
     constexpr int NST = CL ? C::CL_STAGES : C::STAGES;
     unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     float* const red = (float*)(tiles + NST * C::STAGE);                  // cluster mode: [rank - 1][BN][128] sums of the other ranks
@@ -200,7 +230,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int nkb_total = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < NST; s++) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+        for (int s = 0; s < NST; s++) { mbar_init(full + s, 1); mbar_init(empty + s, PAIRS ? 2 : 1); }
         for (int b = 0; b < 2; b++) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 128); }
         mbar_init(red_full, CL ? (n_splits - 1) * 128 : 1);         // one arrival per epilogue thread of every other rank
         *abort_flag = 0;
@@ -217,9 +247,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    if (CL) cluster_sync();                            // every block's barriers exist before another block arrives on them
+    if (CL || PAIRS) cluster_sync();                   // every block's barriers exist before another block arrives on them
     Walk walk_first(stream_k != 0, tiles_m, tiles_n, nkb_total, kb_per_split, n_splits);
     walk_first.cl = CL;
+    walk_first.pairs = PAIRS;
+    if (PAIRS) walk_first.item = blockIdx.x / 2;
     const Walk walk_init = walk_first;
     // Weights are written by no kernel: the first stages' weight tiles are asked for before the wait for the kernel
     // before this one (whose results are the tokens), so a product launched early has them on the way by then.
@@ -256,7 +288,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         mbar_expect_tx(full + s, stage_bytes);
                         tma_load_2d(a, &map_w, (kb0 + i) * BK, n0, full + s);
                     }
-                    tma_load_2d(a + C::A_BYTES, &map_x, (kb0 + i) * BK, m0, full + s);
+                    if (PAIRS) {
+                        // this block's half of the token tile's rows, into both blocks of the pair
+                        const int half = bn / 2, r = (int)(blockIdx.x & 1);
+                        tma_load_2d_pair(a + C::A_BYTES + r * half * (BK * 2), &map_x, (kb0 + i) * BK, m0 + r * half, full + s);
+                    } else {
+                        tma_load_2d(a + C::A_BYTES, &map_x, (kb0 + i) * BK, m0, full + s);
+                    }
                     armed = it + 1;
                 }
             }
@@ -291,7 +329,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     #pragma unroll
                     for (int j = 0; j < BK / 16; j++)
                         umma(acc, umma_desc(a + j * 32), umma_desc(b + j * 32), idesc, (i | j) != 0);
-                    umma_commit(empty + s);             // the stage is free once these MMAs have read it
+                    if (PAIRS) umma_commit_pair(empty + s);    // ... in both blocks, whose copies fill each other's stages
+                    else umma_commit(empty + s);             // the stage is free once these MMAs have read it
                 }
                 if (ok) umma_commit(acc_full + buf);
                 IK_STAMP(4);
@@ -528,7 +567,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
     if (threadIdx.x == 0) IK_STAMP(7);
     // no block of a cluster leaves while another may still store into its shared memory or arrive on its barrier
-    if (CL) cluster_sync();
+    if (CL || PAIRS) cluster_sync();
 }
 
 // Adds the K slices in slice order and writes Y.
@@ -585,7 +624,7 @@ int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int M,
     const long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
     const int per = (nkb + n_cl - 1) / n_cl;
     if (n_cl < 2 || n_cl > C::RED_SLOTS + 1 || (long long)(n_cl - 1) * per >= nkb || tiles * n_cl > max_blocks()) return IK_UNSUPPORTED;
-    auto kern = gemm_tcgen05_kernel<BN, TY, true>;
+    auto kern = gemm_tcgen05_kernel<BN, TY, 1>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::CL_SMEM);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
@@ -610,7 +649,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial
            int accumulate, int swiglu, int splits, int* status, const IkRopeStore& rope, int bn, cudaStream_t stream) {
     typedef Cfg<BN> C;
     if (splits < 0) return launch_cluster<BN, TY>(mw, mx, Y, M, N, K, ldy, accumulate, swiglu, -splits, status, rope, bn, stream);
-    auto kern = gemm_tcgen05_kernel<BN, TY, false>;
+    auto kern = gemm_tcgen05_kernel<BN, TY, 0>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
     if (e != cudaSuccess) return (int)e;
     const int nkb = (K + BK - 1) / BK;
@@ -663,6 +702,69 @@ IK_EXPORT int ik_gemm_tcgen05_tile_width(int M, int N) {
     return best;
 }
 
+#ifdef IK_TCGEN05_PAIRS
+// ------------------------------------------------------------------------------------------
+// The pair mode (this build only): whole tiles, more than 256 tokens, two blocks to a token tile's copy.
+namespace {
+template <typename TY>
+int launch_pairs(const CUtensorMap& mw, const CUtensorMap& mx_half, void* Y, int M, int N, int K, int ldy, int accumulate,
+                 int swiglu, int* status, const IkRopeStore& rope, int bn, cudaStream_t stream) {
+    typedef Cfg<256> C;
+    auto kern = gemm_tcgen05_kernel<256, TY, 2>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    const int nkb = (K + BK - 1) / BK;
+    const long long items = (long long)(((N + BM - 1) / BM + 1) / 2) * ((M + bn - 1) / bn);
+    const long long clusters = items < max_blocks() / 2 ? items : max_blocks() / 2;
+    if (clusters < 1) return IK_UNSUPPORTED;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * clusters));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = C::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (ik_pdl_mask() & IK_FAMILY) ? 2 : 1;
+    IK_RETURN_IF_ERROR(cudaLaunchKernelEx(&cfg, kern, mw, mx_half, (TY*)Y, (float*)nullptr, M, N, K, ldy, accumulate, swiglu, nkb, 1, 0,
+                                          status, rope, bn));
+    return (int)cudaGetLastError();
+}
+
+int pairs_impl(const void* X, const void* W, void* Y, int y_dtype, int M, int N, int K, int ldx, int ldw, int ldy,
+               int accumulate, int swiglu, int* status, const IkRopeStore& rope, cudaStream_t stream) {
+    if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || (!rope.q_out && ldy < (swiglu ? N / 2 : N))) return IK_BAD_ARGUMENT;
+    if (swiglu && ((N & 1) || accumulate)) return IK_BAD_ARGUMENT;
+    if (y_dtype != IK_F32 && y_dtype != IK_BF16) return IK_BAD_ARGUMENT;
+    if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return IK_UNSUPPORTED;
+    if (M <= 256) return IK_UNSUPPORTED;                 // fewer tokens are bound by the weights' bytes: nothing to share
+    const int bn = ik_gemm_tcgen05_tile_width(M, N);
+    CUtensorMap mw, mx;
+    int st = ik_make_map(&mw, W, N, K, ldw, BM);
+    if (st != IK_OK) return st;
+    st = ik_make_map(&mx, X, M, K, ldx, bn / 2);         // a block copies half of a token tile's rows
+    if (st != IK_OK) return st;
+    return y_dtype == IK_F32 ? launch_pairs<float>(mw, mx, Y, M, N, K, ldy, accumulate, swiglu, status, rope, bn, stream)
+                             : launch_pairs<bf16>(mw, mx, Y, M, N, K, ldy, accumulate, swiglu, status, rope, bn, stream);
+}
+}  // namespace
+
+// Arguments as ik_gemm_tcgen05 without the scratch and the way of sharing out; IK_UNSUPPORTED up to 256 tokens.
+IK_EXPORT int ik_gemm_tcgen05_pairs(const void* X, const void* W, void* Y, int y_dtype, int M, int N, int K, int ldx, int ldw,
+                                    int ldy, int accumulate, int swiglu, int* status, cudaStream_t stream) {
+    IkRopeStore none = {};
+    return pairs_impl(X, W, Y, y_dtype, M, N, K, ldx, ldw, ldy, accumulate, swiglu, status, none, stream);
+}
+
+IK_EXPORT int ik_gemm_qkv_rope_tcgen05_pairs(const void* X, const void* W, int M, int N, int K, int ldx, int ldw, int* status,
+                                             const IkRopeStore* rope, cudaStream_t stream) {
+    if (!rope || !rope->q_out || (rope->hd & 1) || N != (rope->nh + 2 * rope->nkv) * rope->hd) return IK_BAD_ARGUMENT;
+    return pairs_impl(X, W, nullptr, IK_F32, M, N, K, ldx, ldw, N, 0, 0, status, *rope, stream);
+}
+#else
 // Scratch of the stream-K mode, in bytes: zeroed once by the caller, then left to the kernels (one stream at a time).
 IK_EXPORT int ik_gemm_tcgen05_stream_k_bytes() { return (int)stream_k_bytes(); }
 
@@ -771,3 +873,4 @@ IK_EXPORT int ik_gemm_tcgen05_timeline(unsigned long long* out /* [1024][8] */) 
     return e == cudaSuccess ? IK_OK : (int)e;
 }
 #endif
+#endif  // IK_TCGEN05_PAIRS

@@ -6,6 +6,7 @@ declared outputs.  A non-zero status from the library raises ``KernelError``.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -406,9 +407,30 @@ def tcgen05_splits(M: int, N: int, K: int) -> int:
     return 1
 
 
+_pairs_lib = None
+PAIRS = os.environ.get("IK_PAIRS", "1") != "0"
+
+
+def pairs_lib():
+    """The pair mode of the tcgen05 product (two blocks share one copy of a token tile: less traffic from L2 at
+    prefill), a library of its own; None where its source is not there or ``IK_PAIRS=0`` says not to use it."""
+    global _pairs_lib
+    if _pairs_lib is None:
+        if not PAIRS or not build.pairs_available():
+            _pairs_lib = False
+        else:
+            l = build.pairs()
+            l.ik_gemm_tcgen05_pairs.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]
+            l.ik_gemm_tcgen05_pairs.restype = _i
+            l.ik_gemm_qkv_rope_tcgen05_pairs.argtypes = [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]
+            l.ik_gemm_qkv_rope_tcgen05_pairs.restype = _i
+            _pairs_lib = l
+    return timed(_pairs_lib) if _pairs_lib else None
+
+
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=torch.float32,
                  accumulate: bool = False, splits: Optional[int] = None,
-                 status: Optional[torch.Tensor] = None, swiglu: bool = False) -> Optional[torch.Tensor]:
+                 status: Optional[torch.Tensor] = None, swiglu: bool = False, pairs: Optional[bool] = None) -> Optional[torch.Tensor]:
     """bfloat16 operands on the tcgen05 tensor cores (TMA-fed, accumulators in TMEM).  Returns None
     when the kernel does not take these sizes (K not a multiple of 8, unaligned rows).
 
@@ -432,6 +454,17 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
         raise KernelError("gemm: the output has the wrong shape")
     if splits is None:
         splits = tcgen05_splits(M, N, K)
+    if splits == 1 and M > 256 and pairs is not False:
+        pl = pairs_lib()
+        if pl is None and pairs:
+            raise KernelError("gemm_tcgen05: the pair mode was asked for but its library is not there")
+        if pl is not None:
+            _work(f"gemm_tcgen05 pairs{' +swiglu' if swiglu else ''} {M}x{N}x{K}", 2 * (M * K + N * K) + M * n_out * out.element_size(), 2 * M * N * K)
+            st = pl.ik_gemm_tcgen05_pairs(_ptr(x), _ptr(w), _ptr(out), _code(out), M, N, K, x.stride(0), w.stride(0),
+                                          out.stride(0), 1 if accumulate else 0, 1 if swiglu else 0, _ptr(status), _stream())
+            if st != -2:
+                _check(st, "gemm_tcgen05 (pairs)")
+                return out
     partial = (stream_k_scratch(x.device) if splits == 0 else
                torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None)
     _work(f"gemm_tcgen05{' +swiglu' if swiglu else ''} {M}x{N}x{K}", 2 * (M * K + N * K) + M * n_out * out.element_size(), 2 * M * N * K)
@@ -494,6 +527,13 @@ def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages
     else:
         if splits is None:
             splits = tcgen05_splits(M, N, K)
+        pl = pairs_lib() if splits == 1 and M > 256 else None
+        if pl is not None:
+            st = pl.ik_gemm_qkv_rope_tcgen05_pairs(_ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), _ptr(status),
+                                                   ctypes.byref(rs), _stream())
+            if st != -2:
+                _check(st, "gemm_qkv_rope (pairs)")
+                return True
         partial = (stream_k_scratch(x.device) if splits == 0 else
                    torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None)
         st = lib().ik_gemm_qkv_rope_tcgen05(_ptr(x), _ptr(w), _ptr(partial), M, N, K, x.stride(0), w.stride(0), splits,

@@ -161,6 +161,30 @@ def test_gemm_tcgen05_cluster_mode_refuses_what_it_does_not_take():
     assert status.item() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 260, 72), (513, 257, 4096), (2048, 4096, 512), (1000, 128, 264), (700, 1300, 1024)])
+@pytest.mark.parametrize("ydt", [torch.float32, torch.bfloat16])
+def test_gemm_tcgen05_pair_mode(M, N, K, ydt):
+    """More than 256 tokens: pairs of blocks take two weight tiles each and share one copy of every token tile (half
+    of its rows fetched by each block into both).  Odd numbers of weight tiles leave a block of the last pair with
+    a tile that does not exist.  The sums run in the same order as without pairs, so the results are the same bits."""
+    if ops().pairs_lib() is None:
+        pytest.skip("the pair mode's library is not part of this checkout")
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    x, w = rnd((M, K), 36, torch.bfloat16).to(DEV), rnd((N, K), 37, torch.bfloat16).to(DEV)
+    ref = x.double().cpu() @ w.double().cpu().T
+    got = ops().gemm_tcgen05(x, w, out_dtype=ydt, splits=1, status=status, pairs=True)
+    assert got is not None and status.item() == 0
+    close(got, ref, 2e-5 if ydt == torch.float32 else 5e-3)
+    plain = ops().gemm_tcgen05(x, w, out_dtype=ydt, splits=1, status=status, pairs=False)
+    assert torch.equal(got, plain)
+    base = rnd((M, N), 38, ydt).to(DEV)
+    acc = ops().gemm_tcgen05(x, w, out=base.clone(), accumulate=True, splits=1, status=status, pairs=True)
+    assert torch.equal(acc, ops().gemm_tcgen05(x, w, out=base.clone(), accumulate=True, splits=1, status=status, pairs=False))
+    for _ in range(3):                                       # back to back: stages and barriers of both blocks stay in step
+        assert torch.equal(ops().gemm_tcgen05(x, w, out_dtype=ydt, splits=1, status=status, pairs=True), got)
+    assert status.item() == 0
+
+
 def test_gemm_tcgen05_stream_k_back_to_back():
     """Stream-K products of different shapes one after another share one scratch: every launch leaves the
     flags as it found them, a tile cut into many pieces (one tile, K = 8192) sums them in K order, and the
@@ -351,6 +375,16 @@ def test_qkv_product_with_rotary_and_cache_epilogue(nh, nkv, hd, T_new):
         close(q3.view(T, nh, hd), q_ref[:, :, order], 6e-3)
         k3h = k3.cpu()
         close(torch.stack([k3h[pg.table[s, p // 64], :, p % 64] for s, p in zip(token_seq, token_pos)]), k_ref[:, :, order], 6e-3)
+        assert status.item() == 0
+    # whole tiles, which more than 256 tokens run in the pair mode where its library is there
+    if T > 256:
+        q4, (k4, v4, _) = torch.zeros_like(q_out), pg.dev()
+        assert ops().gemm_qkv_rope(x.to(DEV), w, q4, k4, v4, cs, torch.from_numpy(token_seq).to(DEV), pos.to(DEV), tab,
+                                   nh, nkv, hd, True, status, splits=1)
+        close(q4.view(T, nh, hd), q_ref[:, :, order], 6e-3)
+        k4h, v4h = k4.cpu(), v4.cpu()
+        close(torch.stack([k4h[pg.table[s, p // 64], :, p % 64] for s, p in zip(token_seq, token_pos)]), k_ref[:, :, order], 6e-3)
+        close(torch.stack([v4h[pg.table[s, p // 64], :, p % 64] for s, p in zip(token_seq, token_pos)]), v_ref, 6e-3)
         assert status.item() == 0
     # without the right to write the cache only q appears
     k2, v2 = torch.zeros_like(k_d), torch.zeros_like(v_d)
