@@ -291,9 +291,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint64_t* k_free = v_full + TC_NS;
     uint64_t* v_free = k_free + TC_NS;
     uint64_t* s_full = v_free + TC_NS;                         // [2]
-    uint64_t* p_ready = s_full + 2;
-    uint64_t* pv_done = p_ready + 1;
-    uint32_t* tmem_slot = (uint32_t*)(pv_done + 1);
+    uint64_t* p_ready = s_full + 2;                            // [2] the probabilities of a page are written: even pages, odd pages
+    uint64_t* pv_done = p_ready + 2;
+    uint64_t* o_done = pv_done + 1;                            // the tile's last product has run: used once, so its parity is 0
+    uint32_t* tmem_slot = (uint32_t*)(o_done + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -303,8 +304,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(k_full + s, 1); mbar_init(v_full + s, 1); mbar_init(k_free + s, 1); mbar_init(v_free + s, 1);
         }
         mbar_init(s_full, 1); mbar_init(s_full + 1, 1);
-        mbar_init(p_ready, 128);
+        mbar_init(p_ready, 128); mbar_init(p_ready + 1, 128);
         mbar_init(pv_done, 1);
+        mbar_init(o_done, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" :: "l"(&map_q) : "memory");
@@ -373,7 +375,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int i = 0; i < n_iter && ok; i++) {
                 if (i + 1 < n_iter) { ok = issue_qk(i + 1); if (!ok) break; }     // runs while page i is in the softmax
                 const int s = i % TC_NS;
-                ok = mbar_wait(p_ready, i & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 15, i) && mbar_wait(v_full + s, (i / TC_NS) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 16, i);
+                ok = mbar_wait(p_ready + (i & 1), (i >> 1) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 15, i) && mbar_wait(v_full + s, (i / TC_NS) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 16, i);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t v_addr = smem_u32(Vs + s * TC_KV_BYTES);
@@ -384,6 +386,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 umma_commit(v_free + s);
                 umma_commit(pv_done);
             }
+            if (ok) umma_commit(o_done);
         }
     } else {
         const int quarter = warp & 3, r = quarter * 32 + lane;
@@ -469,20 +472,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             tmem_st_wait();
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            // p_ready counts arrivals, not threads: nobody arrives for page i before everybody has for page i - 1.
-            // (The scores of page i + 1 can be there before that, so a thread that is ahead would otherwise complete
-            // the phase of one that is behind, and the product would read probabilities not yet written.)
-            if (i > 0) {
-                ok = mbar_wait(p_ready, (i - 1) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 19, i);
-                if (!ok) break;
-            }
-            mbar_arrive(p_ready);
+            // The arrivals of even and of odd pages are counted on barriers of their own.  A barrier counts arrivals,
+            // not threads, and a wait names its phase by parity alone: with one barrier for all pages a thread that is a
+            // page ahead (the scores of page i + 1 can be there before everybody has arrived for page i) would complete
+            // the phase of one that is behind, and the issuing thread could find the barrier two phases on.  On its
+            // own barrier page i meets only pages i - 2 and i + 2: everybody has arrived for page i - 2 before the scores
+            // of page i are even asked for, and the scores of page i + 2 are asked for only after the issuing thread
+            // has seen everybody arrive for page i.
+            mbar_arrive(p_ready + (i & 1));
         }
-        // The last product.  Nothing above has waited for the one before it (it is known to have run only up to two
-        // pages back: the scores of the last page were there), and a parity names a phase only if the phase before
-        // it is over: so that one is waited for first.
-        if (ok && n_iter > 1) ok = mbar_wait(pv_done, (n_iter - 2) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 20, n_iter);
-        if (ok && mbar_wait(pv_done, (n_iter - 1) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 21, n_iter)) {
+        // The last product, on a barrier of its own.  pv_done will not do here: a wait names a phase by its parity, which
+        // is only safe while the barrier can be at most one phase away from the one meant.  Behind its last arrival a
+        // thread knows nothing of pv_done but that it is one or two products short of the end, and while it waits for the
+        // product before the last both may complete: the barrier then stands two phases on, at the same parity again, and
+        // the wait never ends (seen on one box as an expired wait at this place, in tiles of two pages).
+        if (ok && mbar_wait(o_done, 0, abort_flag, status, IK_WAIT_LIMIT_NS, 21, n_iter)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = 1.0f / l;
             bf16* orow = out + ((size_t)(q_begin + row0 + r) * nh + h) * HD;
@@ -724,7 +728,7 @@ IK_EXPORT int ik_attn_head_dim() { return HD; }
 
 // Sites of the tcgen05 prefill kernel's waits: 11, 12 = loader for a free key / value stage; 13 = issuer for the
 // queries; 14 = issuer for keys; 15 = issuer for the probabilities; 16 = issuer for values; 17 = softmax for scores;
-// 18 = softmax for the product before a rescaling; 19 = softmax for the others' arrivals; 20, 21 = the last products.
+// 18 = softmax for the product before a rescaling; 21 = softmax for the tile's last product.
 IK_EXPORT int ik_attn_take_wait_record(int* out4) { return ik_take_wait_record(out4); }
 
 IK_EXPORT int ik_attn_prefill(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_seqlens,
