@@ -470,6 +470,29 @@ def test_attention_tcgen05_many_tiles_of_few_pages(hd, window):
         close(got, c["ref"], 8e-3)
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+def test_attention_tcgen05_thousands_of_two_page_tiles(hd):
+    """Tiles that see exactly two pages, thousands of blocks, many times over.  With two products per tile the wait for
+    the last one once named its phase on a barrier that could by then stand two phases on; it showed on one box
+    only, a few times in ten thousand blocks.  Every run must give the first run's bits and leave the status word clean."""
+    from ithaca_b200.csrc import attention_bf16 as A
+    nh, nkv = 16, 4
+    lens = [128] * 48 + [100] * 32 + [65] * 16
+    c = attention_case(nh, nkv, hd, lens, lens, None, torch.bfloat16, seed=35)
+    k_d, v_d, tab = c["pg"].dev()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    first = None
+    for rep in range(60):
+        got = A.prefill(c["q"], k_d, v_d, c["cu"], c["kv_lens"], tab, len(lens), max(lens), nh, 1 / math.sqrt(hd), 0,
+                        status, kind="tc")
+        if first is None:
+            first = got.clone()
+            close(got, c["ref"], 8e-3)
+        else:
+            assert torch.equal(got, first), rep
+    assert status.item() == 0
+
+
 @pytest.mark.parametrize("nh,nkv,hd", SHAPES)
 @pytest.mark.parametrize("window", [0, 40, 300])
 def test_attention_bf16_decode(nh, nkv, hd, window):
