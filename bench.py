@@ -2,6 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl reference]
     python bench.py --only decode|prefill|attention|products   one part alone (small cases for profiling)
+    python bench.py --only marginal [--batch B]                 what each kernel family costs inside the replayed decode step
     python bench.py --config 1b-unequal|13b-long                the other two workloads alone, through Engine.generate
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at the given batch with every
@@ -420,6 +421,72 @@ def attention_run(cfg, reps):
     return out
 
 
+def marginal_run(eng, cfg, batch, vocab, context, steps=30):
+    """What each kernel family costs inside the graph-replayed decode step: the step is captured again with that
+    family's launches left out (its results are then wrong, its time is what the rest takes) and the difference to the
+    whole step is the family's share, overlap with its neighbours included.  Per layer, in microseconds."""
+    import torch
+    from ithaca_b200.csrc import attention_bf16, gemm_bf16, ops
+    slots = [eng.alloc_slot() for _ in range(batch)]
+    fill_cache(eng, slots, context - 100, vocab, seed=1)
+    dec, toks, layers = eng._decoder, [[7]] * batch, cfg["num_hidden_layers"]
+    d, ff = cfg["hidden_size"], cfg["intermediate_size"]
+    keep = dict(rmsnorm=ops.rmsnorm, decode=attention_bf16.decode, gemm=gemm_bf16.gemm, swiglu=gemm_bf16.gemm_swiglu, qkv=ops.gemm_qkv_rope)
+    bufs = {}
+
+    def buf(key, shape, dtype, dev):
+        if key not in bufs:
+            bufs[key] = torch.zeros(shape, dtype=dtype, device=dev)
+        return bufs[key]
+
+    def no_norm(x, w, eps, out_dtype, rows_in=None, out=None):
+        rows = x.shape[0] if rows_in is None else rows_in.numel()
+        return buf(("n", rows, out_dtype), (rows, x.shape[1]), out_dtype, x.device)
+
+    def no_product(rows, cols):
+        def f(x, w, out=None, accumulate=False, out_dtype=torch.float32):
+            if tuple(w.shape) != (rows, cols):
+                return keep["gemm"](x, w, out=out, accumulate=accumulate, out_dtype=out_dtype)
+            return out if out is not None else buf(("g", x.shape[0], rows), (x.shape[0], rows), out_dtype, x.device)
+        return f
+
+    def timed():
+        dec.graphs.clear()
+        dec.step(slots, toks)
+        for _ in range(5):
+            dec.step(slots, toks)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            dec.step(slots, toks)
+        b.record()
+        torch.cuda.synchronize()
+        for s in slots:
+            eng.truncate(s, eng.length(s) - steps - 6)          # every variant at the same context
+        return a.elapsed_time(b) / steps * 1e3 / layers
+
+    out = {"whole_step": round(timed(), 2)}
+    variants = [("norms", ops, "rmsnorm", no_norm),
+                ("attention_and_merge", attention_bf16, "decode", lambda q, *a, **k: buf(("a", q.shape), q.shape, q.dtype, q.device)),
+                ("o", gemm_bf16, "gemm", no_product(d, cfg["num_attention_heads"] * cfg["head_dim"])),
+                ("down", gemm_bf16, "gemm", no_product(d, ff)),
+                ("gate_up", gemm_bf16, "gemm_swiglu", lambda x, w, out_dtype=torch.bfloat16: buf(("s", x.shape[0]), (x.shape[0], w.shape[0] // 2), out_dtype, x.device)),
+                ("qkv", ops, "gemm_qkv_rope", lambda *a, **k: True)]
+    for name, module, attr, stand_in in variants:
+        original = getattr(module, attr)
+        setattr(module, attr, stand_in)
+        try:
+            out[name] = round(out["whole_step"] - timed(), 2)
+        finally:
+            setattr(module, attr, original)
+    eng.runtime.status.zero_()
+    dec.graphs.clear()
+    for s in slots:
+        eng.free_slot(s)
+    return out
+
+
 def attempt(run, eng=None):
     """One part of the line: run it, once more if it raises, and if it raises again say so in its place.  The other
     parts of the line stand on their own measurements and are printed all the same."""
@@ -461,7 +528,7 @@ def main():
                     help="with --only products: token counts, e.g. 16,32,64: a sweep over the ways the products can run")
     ap.add_argument("--config", default=None, choices=["1b-unequal", "13b-long"],
                     help="run one of the other workloads alone and print its figures")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention", "products"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention", "products", "marginal"],
                     help="run one part only and print its figures (for profiling a small case)")
     args = ap.parse_args()
 
@@ -511,6 +578,10 @@ def main():
     if args.only == "decode":
         r = decode_run(eng, args.batch, args.steps, args.warmup, vocab, CONTEXT)
         print(json.dumps({"only": "decode", "batch": args.batch, "layers": n_layers, **{k: v for k, v in r.items() if k != "clocks"}}))
+        return 0
+    if args.only == "marginal":
+        r = marginal_run(eng, cfg, args.batch, vocab, CONTEXT)
+        print(json.dumps({"only": "marginal", "batch": args.batch, "layers": n_layers, "us_per_layer": r}))
         return 0
     if args.only == "prefill":
         ms = prefill_run(eng, PREFILL_TOKENS, vocab, reps=max(1, args.steps))
