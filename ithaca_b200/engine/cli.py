@@ -47,6 +47,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--peaks", metavar="FILE.json", default=None,
                     help="with --profile: hbm_gbs and bf16_tflops to hold the kernels against (default: measured now)")
     ap.add_argument("--describe", action="store_true", help="print the model's layers and schedule, then exit")
+    ap.add_argument("--selftest", action="store_true",
+                    help="check this installation on the device without a model folder: a small random model whole against "
+                         "token by token (same bits in float32), bfloat16 against float32, the kernels' bounded waits")
     return ap
 
 
@@ -101,8 +104,56 @@ def _profile(eng, prompts: List[List[int]], peaks_file: Optional[str]) -> None:
         eng.free_slot(s)
 
 
+def _selftest() -> int:
+    """The reference's command line carries self-tests of its kernels (``--fatest``, ``--quanttest`` and others,
+    src/main.cpp:986-1031).  This one needs no files: the model is random."""
+    import torch
+    from ..csrc import ops
+    from .api import Engine
+    cfg = {"architectures": ["LlamaForCausalLM"], "hidden_size": 264, "num_hidden_layers": 3, "num_attention_heads": 6,
+           "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 520, "vocab_size": 1003, "rope_theta": 500000.0,
+           "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                            "original_max_position_embeddings": 64},
+           "rms_norm_eps": 1e-5, "max_position_embeddings": 1024, "tie_word_embeddings": True, "torch_dtype": "bfloat16"}
+    ids = [(7 * i * i + 3 * i + 1) % 1003 for i in range(300)]
+    failed = 0
+
+    def report(name: str, ok: bool, detail: str) -> None:
+        nonlocal failed
+        failed += not ok
+        print(f"{'ok  ' if ok else 'FAIL'} {name}: {detail}")
+
+    logits = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_random(cfg, 1, dtype=dtype, max_tokens=1024)
+        s = eng.alloc_slot()
+        whole = eng.step([s], [ids], "all").float()
+        eng.free_slot(s)
+        s = eng.alloc_slot()
+        rows = [eng.step([s], [ids[:130]], "all").float()] + [eng.step([s], [ids[130:261]], "all").float()]
+        rows += [eng.step([s], [[t]], "last").float() for t in ids[261:]]
+        eng.check_status()
+        cut = torch.cat(rows)
+        diff = float((cut - whole).abs().max() / whole.abs().max())
+        report(f"{dtype}: two pieces and 39 single tokens against the whole prompt", diff == 0.0 if dtype == "float32" else diff <= 1e-2,
+               f"largest difference {diff:.3g} of the logits' scale")
+        out = eng.generate([ids[:40], ids[:7]], max_tokens=12, temp=0.0, rep_pen=1.0, stop_token_ids=[])
+        report(f"{dtype}: greedy generation of two requests", all(len(o) == 12 for o in out), f"{out[1]}")
+        logits[dtype] = whole
+    diff = float((logits["bfloat16"] - logits["float32"]).abs().max() / logits["float32"].abs().max())
+    report("bfloat16 against float32", diff <= 2e-2, f"largest difference {diff:.3g} of the logits' scale")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+    res = ops.selftest_wait_expires(status, 1_000_000).cpu().tolist()
+    report("a wait that nothing satisfies gives up", res[0] == 0 and res[1] == 1 and res[3] == 0 and res[5] == 0 and int(status.item()) == 8,
+           f"after {res[2]} us; a second waiter left after {res[4]} us")
+    print("selftest passed" if not failed else f"selftest: {failed} check(s) FAILED")
+    return 1 if failed else 0
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     args = build_parser().parse_args(argv)
+    if args.selftest:
+        return _selftest()
     t0 = time.perf_counter()
     eng = _engine(args)
     load_s = time.perf_counter() - t0
