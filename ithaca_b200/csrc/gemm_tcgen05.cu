@@ -479,6 +479,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             bf16* const kv_base = (rotated ? rope.k_pages : rope.v_pages) +
                                   (size_t)(head - rope.nh - (rotated ? 0 : rope.nkv)) * rope.page_size * rope.hd + r0;
             const float2* const cs_base = reinterpret_cast<const float2*>(rope.cos_sin) + (r0 >> 1);
+            // The plain epilogue (whole sums of this block, to Y or added to Y): 32 columns a turn, both halves of the
+            // accumulator asked for before either is waited for.
+            if (!fused_rope && !swiglu && !slice_sums && !CL && c_hi == c_lo) {
+                #pragma unroll 1
+                for (int c0 = 0; c0 < bn && m0 + c0 < M; c0 += 32) {
+                    float v[32];
+                    const bool second = c0 + 16 < bn && m0 + c0 + 16 < M;
+                    tmem_ld16_issue(acc + c0, v);
+                    if (second) tmem_ld16_issue(acc + c0 + 16, v + 16);
+                    tmem_ld_wait();
+                    if (feature < N) {
+                        #pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            if (h == 1 && !second) break;
+                            if (accumulate) {
+                                #pragma unroll
+                                for (int c = 0; c < 16; c++) v[16 * h + c] += y_ahead[c];
+                                if (c0 + 16 * h + 16 < bn && m0 + c0 + 16 * h + 16 < M) load_y(c0 + 16 * h + 16);
+                            }
+                            #pragma unroll
+                            for (int c = 0; c < 16; c++)
+                                if (m0 + c0 + 16 * h + c < M) ik_st(Y, (size_t)(m0 + c0 + 16 * h + c) * ldy + feature, v[16 * h + c]);
+                        }
+                    }
+                }
+            } else
             #pragma unroll 1
             for (int c0 = 0; c0 < bn; c0 += 16) {
                 if (m0 + c0 >= M) break;
