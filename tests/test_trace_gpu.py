@@ -91,3 +91,31 @@ def test_replay_whole_one_by_one_and_batched(tmp_path, name, dtype):
         whole = modes["whole"]
         for mode, got in modes.items():
             assert float(np.abs(got - whole).max() / np.abs(refs[r]).max()) <= REL_CUT[dtype], (mode, r, p)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_with_a_truncation(tmp_path, dtype):
+    """A request is fed 70 tokens, cut back to 33 by the trace, fed another tail in two pieces beside a second
+    request, and decoded: every logit after the cut belongs to the new sequence."""
+    cfg = TINY["B"]
+    d = make_model_dir(tmp_path, cfg, seed=22)
+    pcfg, tensors = load_plain(d)
+    V = cfg["vocab_size"]
+    first, tail, other = random_ids(70, V, 400), random_ids(41, V, 401), random_ids(12, V, 402)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": first, "want": [69]}, {"id": "b", "tokens": other[:9], "want": [8]}], "end": []},
+        {"step": 1, "truncate": {"a": 33}, "entries": [{"id": "a", "tokens": tail[:30], "want": list(range(30))},
+                                                        {"id": "b", "tokens": [other[9]], "want": [0]}], "end": []},
+        {"step": 2, "entries": [{"id": "a", "tokens": tail[30:40], "want": list(range(10))}, {"id": "b", "tokens": [other[10]], "want": [0]}], "end": []},
+        {"step": 3, "entries": [{"id": "a", "tokens": [tail[40]], "want": [0]}, {"id": "b", "tokens": [other[11]], "want": [0]}], "end": ["a", "b"]},
+    ]
+    out = run_trace(d, dtype, str(tmp_path / f"out_{dtype}"), 256, steps)
+    ref_first = plain_logits(pcfg, tensors, first)
+    ref_new = plain_logits(pcfg, tensors, first[:33] + tail)
+    ref_other = plain_logits(pcfg, tensors, other)
+    scale = np.abs(ref_new).max()
+    assert np.abs(out[0][0] - ref_first[69]).max() / scale <= REL[dtype]
+    got_new = np.concatenate([out[1][:30], out[2][:10], out[3][:1]])
+    assert np.abs(got_new - ref_new[33:]).max() / scale <= REL[dtype]
+    got_other = np.stack([out[0][1], out[1][30], out[2][10], out[3][1]])
+    assert np.abs(got_other - ref_other[8:]).max() / np.abs(ref_other).max() <= REL[dtype]
