@@ -57,12 +57,15 @@ __device__ __forceinline__ void store_out(__nv_bfloat16* Y, size_t o, float v, i
 // NT: 8-token column tiles (M <= 8 NT).  A block owns 16 weight rows; each of its 8 warps takes
 // every 8th group of U 64-wide K blocks, loads all of the group's weights (16 bytes per thread
 // per load, 4 U loads in flight per thread) and tokens, then multiplies.  U trades registers
-// (blocks per SM) for bytes in flight; the host picks it per shape.
-template <int NT, int U, typename TY>
+// (blocks per SM) for bytes in flight; the host picks it per shape.  R = 8: a block owns 8 weight rows (the other half
+// of the 16-row MMA operand is zero and never loaded): twice the blocks for a matrix with so few rows that blocks of 16
+// would leave half the SMs' slots empty.
+template <int NT, int U, typename TY, int R>
 __global__ void __launch_bounds__(256)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, TY* __restrict__ Y,
                    int M, int N, int K, int ldx, int ldw, int ldy, int accumulate, int swiglu, const IkRopeStore rope) {
-    constexpr int R = 16, COLS = 8 * NT;
+    constexpr int COLS = 8 * NT, H = R / 8;
+    static_assert(R == 8 || R == 16, "a block owns 8 or 16 weight rows");
     extern __shared__ float red[];                       // [8 warps][R][COLS]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * R;
@@ -73,10 +76,10 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
         #pragma unroll
         for (int i = 0; i < 4; i++) acc[n][i] = 0.f;
 
-    const __nv_bfloat16* wrow[2];
-    bool wok[2];
+    const __nv_bfloat16* wrow[H];
+    bool wok[H];
     #pragma unroll
-    for (int h = 0; h < 2; h++) {
+    for (int h = 0; h < H; h++) {
         const int row = n0 + h * 8 + g;
         wok[h] = row < N;
         wrow[h] = W + (size_t)(wok[h] ? row : 0) * ldw;
@@ -96,7 +99,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
     // then waits for that kernel's results (the tokens).  Launched early, the wait hides this kernel's start-up.
     bool waited = false;
     for (int blk0 = warp * U; blk0 < nblk; blk0 += 8 * U) {
-        uint4 a[U][2][2], b[U][2][NT];
+        uint4 a[U][2][H], b[U][2][NT];
         #pragma unroll
         for (int u = 0; u < U; u++)
             #pragma unroll
@@ -104,7 +107,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
                 const int k = (blk0 + u) * 64 + c * 32 + t * 8;
                 const bool kok = k < K;                   // K % 8 == 0: the whole 8 are inside
                 #pragma unroll
-                for (int h = 0; h < 2; h++) a[u][c][h] = (kok && wok[h]) ? ld_stream(wrow[h] + k) : zero;
+                for (int h = 0; h < H; h++) a[u][c][h] = (kok && wok[h]) ? ld_stream(wrow[h] + k) : zero;
             }
         if (!waited) { ik_pdl_wait(); waited = true; }
         #pragma unroll
@@ -122,8 +125,9 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
             for (int c = 0; c < 2; c++)
                 #pragma unroll
                 for (int n = 0; n < NT; n++) {
-                    mma_bf16(acc[n], a[u][c][0].x, a[u][c][1].x, a[u][c][0].y, a[u][c][1].y, b[u][c][n].x, b[u][c][n].y);
-                    mma_bf16(acc[n], a[u][c][0].z, a[u][c][1].z, a[u][c][0].w, a[u][c][1].w, b[u][c][n].z, b[u][c][n].w);
+                    const uint4 lo = a[u][c][0], hi = H == 2 ? a[u][c][H - 1] : zero;       // rows g and g + 8
+                    mma_bf16(acc[n], lo.x, hi.x, lo.y, hi.y, b[u][c][n].x, b[u][c][n].y);
+                    mma_bf16(acc[n], lo.z, hi.z, lo.w, hi.w, b[u][c][n].z, b[u][c][n].w);
                 }
     }
     if (!waited) ik_pdl_wait();
@@ -135,8 +139,10 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
         const int col = n * 8 + 2 * t;
         mine[g * COLS + col] = acc[n][0];
         mine[g * COLS + col + 1] = acc[n][1];
-        mine[(g + 8) * COLS + col] = acc[n][2];
-        mine[(g + 8) * COLS + col + 1] = acc[n][3];
+        if (H == 2) {
+            mine[(g + 8) * COLS + col] = acc[n][2];
+            mine[(g + 8) * COLS + col + 1] = acc[n][3];
+        }
     }
     __syncthreads();
     if (rope.q_out) {
@@ -179,12 +185,11 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
     }
 }
 
-template <int NT, int U, typename TY>
+template <int NT, int U, typename TY, int R = 16>
 int launch_skinny(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
                   int accumulate, int swiglu, const IkRopeStore& rope, cudaStream_t stream) {
-    constexpr int R = 16;
     const size_t smem = (size_t)8 * R * 8 * NT * sizeof(float);
-    auto kern = gemm_skinny_kernel<NT, U, TY>;
+    auto kern = gemm_skinny_kernel<NT, U, TY, R>;
     IK_RETURN_IF_ERROR(ik_launch(kern, (N + R - 1) / R, 256, smem, stream, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W,
                                  (TY*)Y, M, N, K, ldx, ldw, ldy, accumulate, swiglu, rope));
     IK_LAUNCH_STATUS();
@@ -196,6 +201,13 @@ bool deep_unroll_pays(int N) {
     const int blocks = (N + 15) / 16, slots = 2 * ik_sm_count();
     const int waves = (blocks + slots - 1) / slots;
     return (double)blocks / ((double)waves * slots) >= 0.8;
+}
+
+// Blocks of 8 rows instead of 16: when blocks of 16 would not even give every SM one (2,048 output features are 128
+// blocks), and K is long enough for a block's eight warps to have work (at least 16 blocks of 64).  Depends on N and K
+// only.  Measured on B200, 8 tokens, 2048 x 8192: see the kernel library's notes.
+bool narrow_blocks_pay(int N, int K) {
+    return (N + 15) / 16 <= ik_sm_count() && K >= 1024;
 }
 
 // ------------------------------------------------------------------------------------------ tiled
@@ -319,6 +331,10 @@ static int gemm_bf16_mma_impl(const void* X, const void* W, void* Y, int y_dtype
                              : launch_skinny<NT, U, __nv_bfloat16>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, swiglu, rope, stream)
     if (skinny) {
         const bool deep = deep_unroll_pays(N);
+        if (M <= 8 && narrow_blocks_pay(N, K)) {
+            return y_dtype == IK_F32 ? launch_skinny<1, 8, float, 8>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, swiglu, rope, stream)
+                                     : launch_skinny<1, 8, __nv_bfloat16, 8>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, swiglu, rope, stream);
+        }
         if (M <= 8) { if (deep) { IK_SK(1, 4); } IK_SK(1, 2); }
         if (M <= 16) { if (deep) { IK_SK(2, 2); } IK_SK(2, 1); }
         if (M <= 32) { IK_SK(4, 1); }

@@ -89,7 +89,8 @@ def test_gemm_simt_rows_do_not_depend_on_batch():
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 64, 64), (8, 200, 72), (9, 4096, 512), (16, 130, 1024), (31, 96, 264),
-                                   (64, 300, 2048), (3, 40, 8)])
+                                   (64, 300, 2048), (3, 40, 8),
+                                   (8, 2048, 8192), (3, 203, 1024), (8, 2368, 1088), (1, 12, 4096)])      # few rows, long K: blocks of 8 rows
 @pytest.mark.parametrize("kind", [1, 2])
 @pytest.mark.parametrize("ydt", [torch.float32, torch.bfloat16])
 def test_gemm_bf16_mma(M, N, K, kind, ydt):
@@ -221,7 +222,7 @@ def test_gemm_tcgen05_strided_rows_and_default_splits():
 
 
 @pytest.mark.parametrize("M", [1, 8, 13, 16, 17, 64, 300])
-@pytest.mark.parametrize("ff,d", [(172, 64), (512, 192), (1000, 264), (4096, 1024)])
+@pytest.mark.parametrize("ff,d", [(172, 64), (512, 192), (1000, 264), (4096, 1024), (600, 1024)])
 def test_gate_up_product_with_swiglu_epilogue(M, ff, d):
     """h = silu(x Wg^T) * (x Wu^T) from one kernel over row-interleaved weights, every dispatch path."""
     from ithaca_b200.csrc import gemm_bf16
@@ -324,12 +325,12 @@ def test_rope_append(nh, nkv, hd, rot, pairing, dtype):
     assert k_h.float().abs().sum(dim=(1, 3))[~touched].max().item() == 0
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(4, 4, 16), (6, 2, 32), (5, 1, 48), (8, 2, 128)])
+@pytest.mark.parametrize("nh,nkv,hd,d", [(4, 4, 16, 264), (6, 2, 32, 264), (5, 1, 48, 264), (8, 2, 128, 264),
+                                         (6, 2, 32, 1024)])      # the last: few rows and a long K, the skinny kernel's blocks of 8 rows
 @pytest.mark.parametrize("T_new", [[3, 5, 1], [20, 7, 30], [40, 30, 66], [300, 2, 70]])
-def test_qkv_product_with_rotary_and_cache_epilogue(nh, nkv, hd, T_new):
+def test_qkv_product_with_rotary_and_cache_epilogue(nh, nkv, hd, d, T_new):
     """x W^T, rotated, with q to its buffer and k, v into the pages, from one kernel: every dispatch path
     (skinny, tcgen05 with whole tiles and stream-K) against the plain product followed by the plain rotation."""
-    d = 264
     new = T_new
     lens = [n + e for n, e in zip(new, (70, 0, 64))]
     T = sum(new)
