@@ -526,6 +526,8 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points and the two other workloads")
     ap.add_argument("--tokens", default=None,
                     help="with --only products: token counts, e.g. 16,32,64: a sweep over the ways the products can run")
+    ap.add_argument("--context", type=int, default=None,
+                    help="with --only decode / prefill: another context length (decode) or prompt length (prefill) than the default run's")
     ap.add_argument("--config", default=None, choices=["1b-unequal", "13b-long"],
                     help="run one of the other workloads alone and print its figures")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention", "products", "marginal"],
@@ -573,19 +575,34 @@ def main():
     per_token = 2 * 2 * n_layers * cfg["num_key_value_heads"] * cfg["head_dim"]
     point_batches = [b for b in point_batches if b * (CONTEXT + 64) * per_token < 100e9]
     max_b = max([args.batch] + point_batches)
-    eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max_b * (CONTEXT + 64), ctx=CONTEXT + 64)
+    context = CONTEXT
+    if args.context and args.only in ("decode", "prefill"):
+        context = args.context
+        if args.only == "decode" and args.batch * (context + 64) * per_token > 100e9:
+            print(f"bench.py: batch {args.batch} at context {context} needs more than 100 GB of cache; not run")
+            return 2
+    layer_flops, head_flops = model_flops_per_token(cfg, n_layers)
+    held = max(context, PREFILL_TOKENS) + 64
+    eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max_b * held, ctx=held,
+                             max_step_tokens=max(16384, context if args.only == "prefill" else 0))
 
     if args.only == "decode":
-        r = decode_run(eng, args.batch, args.steps, args.warmup, vocab, CONTEXT)
-        print(json.dumps({"only": "decode", "batch": args.batch, "layers": n_layers, **{k: v for k, v in r.items() if k != "clocks"}}))
+        r = decode_run(eng, args.batch, args.steps, args.warmup, vocab, context)
+        read = eng.model.weight_bytes() + eng.cache.bytes_per_token() * r["kv_len"] * args.batch
+        print(json.dumps({"only": "decode", "batch": args.batch, "context": context, "layers": n_layers,
+                          "hbm_frac": round(read / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+                          **{k: v for k, v in r.items() if k != "clocks"}}))
         return 0
     if args.only == "marginal":
         r = marginal_run(eng, cfg, args.batch, vocab, CONTEXT)
         print(json.dumps({"only": "marginal", "batch": args.batch, "layers": n_layers, "us_per_layer": r}))
         return 0
     if args.only == "prefill":
-        ms = prefill_run(eng, PREFILL_TOKENS, vocab, reps=max(1, args.steps))
-        print(json.dumps({"only": "prefill", "layers": n_layers, "tokens": PREFILL_TOKENS, "ms": ms}))
+        tokens = args.context or PREFILL_TOKENS
+        ms = prefill_run(eng, tokens, vocab, reps=max(1, args.steps))
+        flops = layer_flops * tokens + head_flops + 4 * cfg["num_attention_heads"] * cfg["head_dim"] * tokens * tokens / 2 * n_layers
+        print(json.dumps({"only": "prefill", "layers": n_layers, "tokens": tokens, "ms": ms, "tok_s": round(tokens / (ms / 1e3), 1),
+                          "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}))
         return 0
 
     clocks = ClockSampler()
@@ -601,7 +618,6 @@ def main():
     e2e = attempt(lambda: e2e_run(eng, args.batch, E2E_STEPS, vocab, CONTEXT), eng)
     pre_ms = prefill_run(eng, PREFILL_TOKENS, vocab)
 
-    layer_flops, head_flops = model_flops_per_token(cfg, n_layers)
     attn_flops = 4 * cfg["num_attention_heads"] * cfg["head_dim"] * PREFILL_TOKENS * PREFILL_TOKENS / 2 * n_layers
     pre_flops = layer_flops * PREFILL_TOKENS + attn_flops + head_flops
     weight_bytes = eng.model.weight_bytes()

@@ -308,8 +308,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc(bn);
-            int it = 0, lt = 0;
+            // One product instruction (128 rows, 16 k) keeps the tensor core busy for about 130 cycles however narrow
+            // the token tile is (measured with the loads left out: 64, 128 and 256 tokens wide all take 0.27-0.3 us per
+            // K step of four), so this thread's own cost per stage matters only for how soon the next stage's products
+            // follow: stage and phase are counted, not divided, and the descriptors are one addition away.
+            const uint32_t idesc = umma_idesc(bn), desc_hi = umma_desc_hi(), a_lo0 = umma_desc_lo(smem_u32(tiles));
+            int it = 0, lt = 0, s = 0;                     // s = it % NST, phase = (it / NST) & 1
+            uint32_t phase = 0;
             bool ok = true;
             Walk walk = walk_init;
             for (Work w; ok && walk.next(w); lt++) {
@@ -319,16 +324,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem_base + buf * C::ACC_COLS;
-                for (int i = 0; i < nkb; i++, it++) {
-                    const int s = it % NST;
-                    ok = mbar_wait(full + s, (it / NST) & 1, abort_flag, status, IK_WAIT_LIMIT_NS, 3, it);
+                for (int i = 0; i < nkb; i++, it++, s = s + 1 == NST ? 0 : s + 1, phase ^= (uint32_t)(s == 0)) {
+                    ok = mbar_wait(full + s, phase, abort_flag, status, IK_WAIT_LIMIT_NS, 3, it);
                     if (!ok) break;
                     if (it == 0) IK_STAMP(3);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a = smem_u32(tiles + s * C::STAGE), b = a + C::A_BYTES;
+                    const uint32_t a_lo = a_lo0 + (uint32_t)s * (C::STAGE >> 4), b_lo = a_lo + (C::A_BYTES >> 4);
                     #pragma unroll
-                    for (int j = 0; j < BK / 16; j++)
-                        umma(acc, umma_desc(a + j * 32), umma_desc(b + j * 32), idesc, (i | j) != 0);
+                    for (int j = 0; j < BK / 16; j++)              // 16 k = 32 bytes = 2 units of the descriptor's address
+                        umma_halves(acc, a_lo + 2 * j, b_lo + 2 * j, desc_hi, idesc, (i | j) != 0);
                     if (PAIRS) umma_commit_pair(empty + s);    // ... in both blocks, whose copies fill each other's stages
                     else umma_commit(empty + s);             // the stage is free once these MMAs have read it
                 }
@@ -708,21 +712,23 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial
 
 }  // namespace
 
-// The room a token tile has for M tokens (the kernel's variant): 32, 64, 128 or 256 tokens.
+// The room a token tile of that width has (the kernel's variant): 32, 64, 128 or 256 tokens.
 IK_EXPORT int ik_gemm_tcgen05_tile(int M) { return M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 
-// The width of token tile in use for M tokens and N output features: a multiple of 16 up to the room.  Up to 256
-// tokens: the tokens rounded up.  Beyond: of the widths from 192 to 256, the one with which the tiles fill the rounds
-// of the persistent grid best (a round costs about as much as the bytes a block loads per K step, 128 + width rows):
-// 2,048 tokens and 4,096 features are 256 tiles of 256 (two rounds on 148 SMs, the second 73 % full) or 288 tiles of 240.
+// The width of token tile in use for M tokens and N output features: a multiple of 16.  Up to 256 tokens: the tokens
+// rounded up (one token tile; few tiles fill the SMs by slicing K).  Beyond: of the widths from 64 to 256, the one whose
+// tiles need the fewest rounds of the persistent grid, a tile costing nearly the same whatever its width (the tensor
+// core is busy for a K step's four instructions just as long with 64 tokens as with 256; loads and epilogue grow
+// with the width): 512 tokens and 4,096 features are 64 tiles of 256, which leave more than half of the SMs idle, or
+// 128 tiles of 128, in one round either way; 2,048 tokens are 256 tiles of 256 or 288 of 240, two rounds either way.
 IK_EXPORT int ik_gemm_tcgen05_tile_width(int M, int N) {
     if (M <= 256) return M <= 16 ? 16 : (M + 15) / 16 * 16;
     const long long tiles_n = (N + BM - 1) / BM, sms = max_blocks();
     int best = 256;
     long long best_cost = -1;
-    for (int bn = 256; bn >= 192; bn -= 16) {
+    for (int bn = 256; bn >= 64; bn -= 16) {
         const long long rounds = (tiles_n * ((M + bn - 1) / bn) + sms - 1) / sms;
-        const long long cost = rounds * (bn + BM);
+        const long long cost = rounds * (1024 + bn);
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
     }
     return best;
@@ -768,6 +774,7 @@ int pairs_impl(const void* X, const void* W, void* Y, int y_dtype, int M, int N,
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return IK_UNSUPPORTED;
     if (M <= 256) return IK_UNSUPPORTED;                 // fewer tokens are bound by the weights' bytes: nothing to share
     const int bn = ik_gemm_tcgen05_tile_width(M, N);
+    if (bn <= 128) return IK_UNSUPPORTED;                // narrow tiles (few weight tiles to fill the SMs with): the variant with their room
     CUtensorMap mw, mx;
     int st = ik_make_map(&mw, W, N, K, ldw, BM);
     if (st != IK_OK) return st;
@@ -810,7 +817,8 @@ static int gemm_tcgen05_impl(const void* X, const void* W, void* Y, int y_dtype,
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return IK_UNSUPPORTED;
     if (splits != 1 && splits >= 0 && !partial) return IK_BAD_ARGUMENT;
     if (M == 0) return IK_OK;
-    const int room = ik_gemm_tcgen05_tile(M), bn = ik_gemm_tcgen05_tile_width(M, N);
+    if (splits < 0 && M > 128) return IK_UNSUPPORTED;     // the cluster mode is for one token tile of at most 128 tokens
+    const int bn = ik_gemm_tcgen05_tile_width(M, N), room = ik_gemm_tcgen05_tile(bn);
     CUtensorMap mw, mx;
     int st = ik_make_map(&mw, W, N, K, ldw, BM);
     if (st != IK_OK) return st;
