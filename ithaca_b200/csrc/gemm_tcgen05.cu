@@ -69,6 +69,7 @@ constexpr int THREADS = 192;
 template <int BN> struct Cfg {
     static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE = A_BYTES + B_BYTES;
     static constexpr int STAGES = (200 * 1024 / STAGE) > 8 ? 8 : (200 * 1024 / STAGE);
+    static constexpr int STAGES2 = 200 * 1024 / (2 * STAGE);    // stages that hold two K blocks each (MODE 3)
     static constexpr int ACC_COLS = BN < 32 ? 32 : BN;           // TMEM columns of one accumulator
     static constexpr int TMEM_COLS = 2 * ACC_COLS;               // two accumulators: one is drained while the other fills
     static constexpr int SMEM = STAGES * STAGE + 1024 /* alignment slack */ + 256 /* barriers */;
@@ -199,6 +200,9 @@ __device__ unsigned long long ik_timeline[1024][8];
 // the MMA warp already fills the other buffer with tile i + 1.
 // MODE 1 (CL): the cluster mode described at the top (n_splits blocks per tile, partial == nullptr, one piece of work
 // per block).  MODE 2 (PAIRS): pairs of blocks share the token tile's copy (whole tiles only; map_x's box is half a tile).
+// MODE 3: as MODE 0 with two K blocks (128 k) per stage.  With narrow token tiles the K loop is bound by what the two
+// feeding threads do per stage (a wait, a fence, a commit: about as long as the stage's four products take), not by the
+// tensor core; eight products per stage halve that share.  A stage then holds [W block 0][W block 1][X block 0][X block 1].
 template <int BN, typename TY, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -208,15 +212,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // loaded per stage and the products are bn columns wide; BN is the room a stage and an accumulator have.
     typedef Cfg<BN> C;
     constexpr bool CL = MODE == 1, PAIRS = MODE == 2;
+    constexpr int KSUB = MODE == 3 ? 2 : 1;            // K blocks of 64 per stage
     extern __shared__ unsigned char smem_raw[];
     __shared__ int rope_rows[4][BN];                   // per epilogue warp: the cache row of each of the tile's tokens
     if (threadIdx.x == 0) IK_STAMP(0);
     // (in cluster mode every block goes on to the cluster's barrier below; its waits are bounded all the same)
     if (!CL && !PAIRS && ik_status_has(status, IK_STATUS_GEMM_TIMEOUT)) return;     // an earlier block gave up
-    constexpr int NST = CL ? C::CL_STAGES : C::STAGES;
+    constexpr int NST = CL ? C::CL_STAGES : KSUB == 2 ? C::STAGES2 : C::STAGES;
+    constexpr int STAGE = KSUB * C::STAGE;             // bytes from one stage to the next
     unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    float* const red = (float*)(tiles + NST * C::STAGE);                  // cluster mode: [rank - 1][BN][128] sums of the other ranks
-    uint64_t* full = (uint64_t*)(tiles + NST * C::STAGE + (CL ? C::RED_BYTES : 0));
+    float* const red = (float*)(tiles + NST * STAGE);                     // cluster mode: [rank - 1][BN][128] sums of the other ranks
+    uint64_t* full = (uint64_t*)(tiles + NST * STAGE + (CL ? C::RED_BYTES : 0));
     uint64_t* empty = full + NST;
     uint64_t* acc_full = empty + NST;                  // [2] accumulator written, ready to be drained
     uint64_t* acc_empty = acc_full + 2;                // [2] accumulator drained, free to be overwritten
@@ -226,7 +232,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_n = (N + BM - 1) / BM, tiles_m = (M + bn - 1) / bn;
-    const int stage_bytes = C::A_BYTES + bn * BK * 2;
+    const int block_bytes = C::A_BYTES + bn * BK * 2;  // what one K block brings: 128 weight rows and bn token rows of 64 k
     const int nkb_total = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -259,9 +265,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (threadIdx.x == 0) {
         Walk walk = walk_init;
         for (Work w; pre_issued < NST && walk.next(w);)
-            for (int i = 0; i < w.nkb && pre_issued < NST; i++, pre_issued++) {
-                mbar_expect_tx(full + pre_issued, stage_bytes);
-                tma_load_2d(tiles + pre_issued * C::STAGE, &map_w, (w.kb0 + i) * BK, w.nt * BM, full + pre_issued);
+            for (int i = 0; i < w.nkb && pre_issued < NST; i += KSUB, pre_issued++) {
+                const int n_sub = min(KSUB, w.nkb - i);
+                mbar_expect_tx(full + pre_issued, n_sub * block_bytes);
+                for (int sub = 0; sub < n_sub; sub++)
+                    tma_load_2d(tiles + pre_issued * STAGE + sub * C::A_BYTES, &map_w, (w.kb0 + i + sub) * BK, w.nt * BM, full + pre_issued);
             }
     }
     if (threadIdx.x == 0) IK_STAMP(1);
@@ -280,20 +288,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             Walk walk = walk_init;
             for (Work w; ok && walk.next(w);) {
                 const int n0 = w.nt * BM, m0 = w.mt * bn, kb0 = w.kb0, nkb = w.nkb;
-                for (int i = 0; i < nkb; i++, it++) {
-                    const int s = it % NST;
-                    unsigned char* a = tiles + s * C::STAGE;
+                for (int i = 0; i < nkb; i += KSUB, it++) {
+                    const int s = it % NST, n_sub = min(KSUB, nkb - i);
+                    unsigned char* a = tiles + s * STAGE;
                     if (it >= pre_issued) {             // the first stages are armed and their weights asked for already
                         if (!mbar_wait(empty + s, ((it / NST) & 1) ^ 1, abort_flag, status, IK_WAIT_LIMIT_NS, 1, it)) { ok = false; break; }
-                        mbar_expect_tx(full + s, stage_bytes);
-                        tma_load_2d(a, &map_w, (kb0 + i) * BK, n0, full + s);
+                        mbar_expect_tx(full + s, n_sub * block_bytes);
+                        for (int sub = 0; sub < n_sub; sub++)
+                            tma_load_2d(a + sub * C::A_BYTES, &map_w, (kb0 + i + sub) * BK, n0, full + s);
                     }
                     if (PAIRS) {
                         // this block's half of the token tile's rows, into both blocks of the pair
                         const int half = bn / 2, r = (int)(blockIdx.x & 1);
                         tma_load_2d_pair(a + C::A_BYTES + r * half * (BK * 2), &map_x, (kb0 + i) * BK, m0 + r * half, full + s);
                     } else {
-                        tma_load_2d(a + C::A_BYTES, &map_x, (kb0 + i) * BK, m0, full + s);
+                        for (int sub = 0; sub < n_sub; sub++)
+                            tma_load_2d(a + KSUB * C::A_BYTES + sub * C::B_BYTES, &map_x, (kb0 + i + sub) * BK, m0, full + s);
                     }
                     armed = it + 1;
                 }
@@ -324,15 +334,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem_base + buf * C::ACC_COLS;
-                for (int i = 0; i < nkb; i++, it++, s = s + 1 == NST ? 0 : s + 1, phase ^= (uint32_t)(s == 0)) {
+                for (int i = 0; i < nkb; i += KSUB, it++, s = s + 1 == NST ? 0 : s + 1, phase ^= (uint32_t)(s == 0)) {
                     ok = mbar_wait(full + s, phase, abort_flag, status, IK_WAIT_LIMIT_NS, 3, it);
                     if (!ok) break;
                     if (it == 0) IK_STAMP(3);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_lo = a_lo0 + (uint32_t)s * (C::STAGE >> 4), b_lo = a_lo + (C::A_BYTES >> 4);
+                    const uint32_t a_lo = a_lo0 + (uint32_t)s * (STAGE >> 4), b_lo = a_lo + ((KSUB * C::A_BYTES) >> 4);
                     #pragma unroll
-                    for (int j = 0; j < BK / 16; j++)              // 16 k = 32 bytes = 2 units of the descriptor's address
-                        umma_halves(acc, a_lo + 2 * j, b_lo + 2 * j, desc_hi, idesc, (i | j) != 0);
+                    for (int sub = 0; sub < KSUB; sub++) {
+                        if (sub > 0 && i + sub >= nkb) break;      // an odd number of K blocks: the last stage holds one
+                        #pragma unroll
+                        for (int j = 0; j < BK / 16; j++)          // 16 k = 32 bytes = 2 units of the descriptor's address
+                            umma_halves(acc, a_lo + sub * (C::A_BYTES >> 4) + 2 * j, b_lo + sub * (C::B_BYTES >> 4) + 2 * j, desc_hi,
+                                        idesc, (i | sub | j) != 0);
+                    }
                     if (PAIRS) umma_commit_pair(empty + s);    // ... in both blocks, whose copies fill each other's stages
                     else umma_commit(empty + s);             // the stage is free once these MMAs have read it
                 }
@@ -695,6 +710,15 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial
     const int n_splits = (nkb + per - 1) / per;
     const long long total = tiles * n_splits;
     const int blocks = (int)(total < max_blocks() ? total : max_blocks());
+    if (n_splits == 1 && BN <= 128 && M > 128) {
+        // whole narrow tiles of a product with several token tiles (compute-bound, few weight tiles): two K blocks a stage
+        auto kern2 = gemm_tcgen05_kernel<BN <= 128 ? BN : 128, TY, 3>;
+        e = cudaFuncSetAttribute(kern2, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        IK_RETURN_IF_ERROR(ik_launch(kern2, blocks, THREADS, C::SMEM, stream, mw, mx, (TY*)Y, (float*)nullptr, M, N, K, ldy, accumulate,
+                                     swiglu, per, 1, 0, status, rope, bn));
+        return (int)cudaGetLastError();
+    }
     IK_RETURN_IF_ERROR(ik_launch(kern, blocks, THREADS, C::SMEM, stream, mw, mx, (TY*)Y, n_splits > 1 ? partial : nullptr, M,
                                  N, K, ldy, accumulate, swiglu, per, n_splits, 0, status, rope, bn));
     e = cudaGetLastError();
@@ -715,14 +739,14 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial
 // The room a token tile of that width has (the kernel's variant): 32, 64, 128 or 256 tokens.
 IK_EXPORT int ik_gemm_tcgen05_tile(int M) { return M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 
-// The width of token tile in use for M tokens and N output features: a multiple of 16.  Up to 256 tokens: the tokens
+// The width of token tile in use for M tokens and N output features: a multiple of 16.  Up to 128 tokens: the tokens
 // rounded up (one token tile; few tiles fill the SMs by slicing K).  Beyond: of the widths from 64 to 256, the one whose
 // tiles need the fewest rounds of the persistent grid, a tile costing nearly the same whatever its width (the tensor
 // core is busy for a K step's four instructions just as long with 64 tokens as with 256; loads and epilogue grow
 // with the width): 512 tokens and 4,096 features are 64 tiles of 256, which leave more than half of the SMs idle, or
 // 128 tiles of 128, in one round either way; 2,048 tokens are 256 tiles of 256 or 288 of 240, two rounds either way.
 IK_EXPORT int ik_gemm_tcgen05_tile_width(int M, int N) {
-    if (M <= 256) return M <= 16 ? 16 : (M + 15) / 16 * 16;
+    if (M <= 128) return M <= 16 ? 16 : (M + 15) / 16 * 16;
     const long long tiles_n = (N + BM - 1) / BM, sms = max_blocks();
     int best = 256;
     long long best_cost = -1;
