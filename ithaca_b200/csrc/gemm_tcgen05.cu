@@ -200,9 +200,14 @@ __device__ unsigned long long ik_timeline[1024][8];
 // the MMA warp already fills the other buffer with tile i + 1.
 // MODE 1 (CL): the cluster mode described at the top (n_splits blocks per tile, partial == nullptr, one piece of work
 // per block).  MODE 2 (PAIRS): pairs of blocks share the token tile's copy (whole tiles only; map_x's box is half a tile).
-// MODE 3: as MODE 0 with two K blocks (128 k) per stage.  With narrow token tiles the K loop is bound by what the two
-// feeding threads do per stage (a wait, a fence, a commit: about as long as the stage's four products take), not by the
-// tensor core; eight products per stage halve that share.  A stage then holds [W block 0][W block 1][X block 0][X block 1].
+// MODE 3: as MODE 0 with two K blocks (128 k) per stage, for token tiles up to 128 wide.  Measured with one thread issuing
+// back to back in a kernel that does nothing else: a product instruction costs the issuing thread 71 cycles and a commit
+// 244, whatever the tile's width, while the tensor core needs 32 / 64 / 128 cycles for 64 / 128 / 256 tokens.  At 256 tokens
+// four products and a commit per K block just keep up (528 against 512 cycles); below that the issuing thread would be
+// the bound, and eight products per commit make it cheaper.  (Two issuing threads, each with an accumulator of its own,
+// issue twice as fast in that kernel, but did not speed up this one: with stages this large only three or four are in
+// flight, and what a block can take in, 192 KB per load latency, is the bound that is left.)
+// A stage holds [W block 0][W block 1][X block 0][X block 1].
 template <int BN, typename TY, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -318,10 +323,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // One product instruction (128 rows, 16 k) keeps the tensor core busy for about 130 cycles however narrow
-            // the token tile is (measured with the loads left out: 64, 128 and 256 tokens wide all take 0.27-0.3 us per
-            // K step of four), so this thread's own cost per stage matters only for how soon the next stage's products
-            // follow: stage and phase are counted, not divided, and the descriptors are one addition away.
+            // With the loads compiled out, a K block of four products and a commit takes this thread 0.27-0.3 us whether
+            // the token tile is 64, 128 or 256 wide (see MODE 3 above), so what it does besides is kept short: stage and
+            // phase are counted, not divided, and the descriptors are one addition away.
             const uint32_t idesc = umma_idesc(bn), desc_hi = umma_desc_hi(), a_lo0 = umma_desc_lo(smem_u32(tiles));
             int it = 0, lt = 0, s = 0;                     // s = it % NST, phase = (it / NST) & 1
             uint32_t phase = 0;
