@@ -530,7 +530,7 @@ def main():
                     help="with --only decode / prefill: another context length (decode) or prompt length (prefill) than the default run's")
     ap.add_argument("--config", default=None, choices=["1b-unequal", "13b-long"],
                     help="run one of the other workloads alone and print its figures")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention", "products", "marginal"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention", "products", "marginal", "issue-rate"],
                     help="run one part only and print its figures (for profiling a small case)")
     args = ap.parse_args()
 
@@ -554,6 +554,14 @@ def main():
         return 0
     shape_name, shape_cfg = SHAPES[args.shape]
     cfg = dict(shape_cfg)
+    if args.only == "issue-rate":
+        # what the thread that issues tensor-core products costs: cycles per instruction, one or two issuing threads
+        from ithaca_b200.csrc import ops
+        status = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+        rows = [{"tokens": n, "per_commit": per, "issuers": k, "cycles_per_instruction": round(ops.tcgen05_issue_rate(n, per, k, status), 1)}
+                for k in (1, 2) for n in (64, 128, 256) for per in (4, 8, 16)]
+        print(json.dumps({"only": "issue-rate", "tensor_core_cycles": {"64": 32, "128": 64, "256": 128}, "rows": rows, "status": int(status.item())}))
+        return 0
     if args.only == "products" and args.tokens:
         counts = [int(t) for t in args.tokens.split(",")]
         print(json.dumps({"only": "products", "model": shape_name, "sweep": products_sweep(cfg, counts, reps=max(3, min(args.steps, 20)))}))

@@ -201,10 +201,10 @@ __device__ unsigned long long ik_timeline[1024][8];
 // MODE 1 (CL): the cluster mode described at the top (n_splits blocks per tile, partial == nullptr, one piece of work
 // per block).  MODE 2 (PAIRS): pairs of blocks share the token tile's copy (whole tiles only; map_x's box is half a tile).
 // MODE 3: as MODE 0 with two K blocks (128 k) per stage, for token tiles up to 128 wide.  Measured with one thread issuing
-// back to back in a kernel that does nothing else: a product instruction costs the issuing thread 71 cycles and a commit
-// 244, whatever the tile's width, while the tensor core needs 32 / 64 / 128 cycles for 64 / 128 / 256 tokens.  At 256 tokens
-// four products and a commit per K block just keep up (528 against 512 cycles); below that the issuing thread would be
-// the bound, and eight products per commit make it cheaper.  (Two issuing threads, each with an accumulator of its own,
+// back to back in a kernel that does nothing else (ik_gemm_tcgen05_issue_rate below): a product instruction costs the
+// issuing thread about 75 cycles and a commit about 190, whatever the tile's width, while the tensor core needs 32 / 64 /
+// 128 cycles for 64 / 128 / 256 tokens.  At 256 tokens four products and a commit per K block just keep up (about 490
+// against 512 cycles); below that the issuing thread would be the bound, and eight products per commit make it cheaper.  (Two issuing threads, each with an accumulator of its own,
 // issue twice as fast in that kernel, but did not speed up this one: with stages this large only three or four are in
 // flight, and what a block can take in, 192 KB per load latency, is the bound that is left.)
 // A stage holds [W block 0][W block 1][X block 0][X block 1].
@@ -913,6 +913,70 @@ __global__ void wait_expiry_kernel(int* status, int* result, const int* never_se
     }
 }
 }  // namespace
+
+// ------------------------------------------------------------------------------------------
+// What issuing costs: `issuers` threads (1 or 2, in warps of their own) each issue `rounds` x `per_commit` product
+// instructions (128 rows, 16 k, n tokens) back to back into an accumulator of their own, with a commit to a barrier of
+// its own after every `per_commit`, over shared memory that holds ones; nothing is loaded meanwhile.
+// out[0] = cycles of this SM's clock until the slowest thread's last commit has completed, out[1] = 1 if all waits ended.
+namespace {
+constexpr int RATE_ROUNDS = 64;
+__global__ void __launch_bounds__(128, 1) issue_rate_kernel(int n, int per_commit, int issuers, long long* out, int* status) {
+    extern __shared__ __align__(1024) unsigned char rate_smem[];
+    __shared__ uint64_t bars[2 * RATE_ROUNDS];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    __shared__ long long cycles[2];
+    __shared__ int fine[2];
+    unsigned char* tiles = (unsigned char*)(((uintptr_t)rate_smem + 1023) & ~(uintptr_t)1023);
+    for (int i = threadIdx.x; i < 160 * 1024 / 4; i += blockDim.x) ((uint32_t*)tiles)[i] = 0x3f803f80u;      // bfloat16 ones
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2 * RATE_ROUNDS; i++) mbar_init(bars + i, 1);
+        abort_flag = 0; cycles[0] = cycles[1] = 0; fine[0] = fine[1] = 1;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (threadIdx.x < 32) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // the ones above are read by the tensor core
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_slot;
+    if ((threadIdx.x & 31) == 0 && (int)(threadIdx.x >> 5) < issuers) {
+        const int me = threadIdx.x >> 5;
+        const uint32_t idesc = umma_idesc(n), a0 = smem_u32(tiles), b0 = a0 + 64 * 1024;
+        const long long t0 = clock64();
+        for (int r = 0; r < RATE_ROUNDS; r++) {
+            for (int u = 0; u < per_commit; u++) {
+                const uint32_t off = (uint32_t)((u & 3) * 32 + ((u >> 2) & 3) * 16384);       // other k, other K block
+                umma(tmem + me * 256, umma_desc(a0 + off), umma_desc(b0 + off), idesc, 1);
+            }
+            umma_commit(bars + me * RATE_ROUNDS + r);       // each barrier is used once
+        }
+        fine[me] = mbar_wait(bars + me * RATE_ROUNDS + RATE_ROUNDS - 1, 0, &abort_flag, status, 100000000ull) ? 1 : 0;   // commits complete in order
+        cycles[me] = clock64() - t0;
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x == 0) { out[0] = cycles[0] > cycles[1] ? cycles[0] : cycles[1]; out[1] = fine[0] && fine[1]; }
+    if (threadIdx.x < 32) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(512u) : "memory");
+    }
+}
+}  // namespace
+
+// Cycles per product instruction of one issuing thread (and, with two, of both together: divide by two) for token
+// tiles n wide; see issue_rate_kernel.  n: a multiple of 16 up to 256; per_commit 1..16; issuers 1 or 2.
+IK_EXPORT int ik_gemm_tcgen05_issue_rate(int n, int per_commit, int issuers, long long* out2, int* status, cudaStream_t stream) {
+    if (n < 16 || n > 256 || n % 16 || per_commit < 1 || per_commit > 16 || issuers < 1 || issuers > 2 || !out2) return IK_BAD_ARGUMENT;
+    cudaError_t e = cudaFuncSetAttribute(issue_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    issue_rate_kernel<<<1, 128, 200 * 1024, stream>>>(n, per_commit, issuers, out2, status);
+    IK_LAUNCH_STATUS();
+}
 
 // Sites of the product's waits: 1 = loader for a free stage, 2 = MMA issuer for a drained accumulator, 3 = MMA issuer
 // for a loaded stage, 4 = epilogue for a finished accumulator, 5 = stream-K gather for another block's piece; 99 = self-test.

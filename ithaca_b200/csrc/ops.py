@@ -88,6 +88,7 @@ _SIGNATURES = {
     "ik_argmax": [_vp, _i, _vp, _i, _i, _vp, _vp],
     "ik_argmax_scratch_bytes": [],
     "ik_selftest_wait_expires": [_vp, _vp, _vp, _u64, _vp],
+    "ik_gemm_tcgen05_issue_rate": [_i, _i, _i, _vp, _vp, _vp],
     "ik_gemm_tcgen05_take_wait_record": [_vp],
     "ik_sample": [_vp, _i, _vp, _vp, _i, _i, _f, _i, _f, _f, _vp, _i, _u64, _vp, _vp, _vp],
 }
@@ -588,6 +589,18 @@ def selftest_wait_expires(status: torch.Tensor, limit_ns: int = 1_000_000) -> to
     never = torch.zeros(1, dtype=torch.int32, device=status.device)
     _check(lib().ik_selftest_wait_expires(_ptr(status), _ptr(result), _ptr(never), limit_ns, _stream()), "selftest_wait_expires")
     return result
+
+
+def tcgen05_issue_rate(n: int, per_commit: int, issuers: int, status: torch.Tensor) -> float:
+    """Cycles of the SM clock per tcgen05 product instruction (128 rows, 16 k, ``n`` tokens) when ``issuers`` threads (1 or
+    2) issue them back to back, ``per_commit`` between commits, and nothing else runs: what the issuing thread costs.
+    With two threads the figure is per thread; together they issue twice as many."""
+    out = torch.zeros(2, dtype=torch.int64, device=status.device)
+    _check(lib().ik_gemm_tcgen05_issue_rate(n, per_commit, issuers, _ptr(out), _ptr(status), _stream()), "tcgen05_issue_rate")
+    cycles, fine = (int(v) for v in out.tolist())
+    if not fine:
+        raise KernelError("tcgen05_issue_rate: a wait ran out")
+    return cycles / (64 * per_commit)
 
 
 _argmax_scratch = {}

@@ -186,6 +186,20 @@ def test_gemm_tcgen05_pair_mode(M, N, K, ydt):
     assert status.item() == 0
 
 
+def test_tcgen05_issue_rate_measurement():
+    """The measurement of what issuing costs runs, ends within its bounded waits, and shows the two facts the product's
+    modes rest on: a 256-wide product instruction keeps the tensor core busy for about 128 cycles, and narrow ones are
+    bound by the issuing thread, so that two threads issue them about twice as fast."""
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    wide = ops().tcgen05_issue_rate(256, 8, 1, status)
+    narrow = ops().tcgen05_issue_rate(64, 8, 1, status)
+    narrow2 = ops().tcgen05_issue_rate(64, 8, 2, status)
+    assert status.item() == 0
+    assert 120 <= wide <= 160, wide
+    assert 40 <= narrow <= wide, narrow
+    assert narrow2 / 2 < 0.7 * narrow, (narrow, narrow2)
+
+
 def test_gemm_tcgen05_stream_k_back_to_back():
     """Stream-K products of different shapes one after another share one scratch: every launch leaves the
     flags as it found them, a tile cut into many pieces (one tile, K = 8192) sums them in K order, and the
